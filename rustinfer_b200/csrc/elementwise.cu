@@ -1,0 +1,205 @@
+// Row-wise kernels of the decoder: embedding gather, residual add + RMSNorm, rotary
+// position encoding fused with the write of keys and values into cache pages, and
+// SiLU-multiply.  All arithmetic is fp32; storage is fp32 or bf16 by template.
+//
+// What they compute follows RustInfer's kernels: embedding
+// (crates/infer-backend-cuda/src/kernels/embedding/emb.cu:9-38), fused add + RMSNorm
+// (crates/infer-backend-cuda/src/kernels/fused_add_rmsnorm/fused_add_rmsnorm.cu:16-97),
+// rotate-half RoPE (crates/infer-backend-cuda/src/kernels/rope/rope.cu:84-133), paged
+// scatter (crates/infer-backend-cuda/src/kernels/kv_cache/scatter_kv_batch.cu:236-300)
+// and SwiGLU (crates/infer-backend-cuda/src/kernels/swiglu/swiglu.cu:294-343).  Unlike
+// them the residual stream stays fp32, the norm's scale is never rounded to bf16, and
+// RoPE and the scatter are one kernel.
+#include "common.cuh"
+
+RI_API const char* ri_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
+
+// ---------------------------------------------------------------- embedding gather
+template <typename TW>
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
+                                    float* __restrict__ out, int d, int vocab) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * d;
+    if (id < 0 || id >= vocab) {            // ids are validated on the host; never read outside
+        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const TW* src = table + (size_t)id * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<TW>(src[i]);
+}
+
+RI_API int ri_embed_gather(const int* ids, const void* table, int table_dtype, float* out,
+                           int tokens, int d, int vocab, void* stream) {
+    if (tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == RI_BF16)
+        embed_gather_kernel<bf16><<<tokens, threads, 0, s>>>(ids, (const bf16*)table, out, d, vocab);
+    else
+        embed_gather_kernel<float><<<tokens, threads, 0, s>>>(ids, (const float*)table, out, d, vocab);
+    return ri_launch_status();
+}
+
+// ------------------------------------------------------- residual add + RMSNorm
+// h (fp32 residual stream) += delta, then out = h * rsqrt(mean(h^2) + eps) * w.
+// With `rows` the kernel reads rows[r] of h and delta, writes row r of out and leaves h
+// alone (the final norm over the rows whose logits are wanted).
+template <typename TA, typename TW>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__ delta,
+                                   const TW* __restrict__ w, float eps, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int d) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* hp = h + (size_t)src * d;
+    const TA* dp = delta ? delta + (size_t)src * d : nullptr;
+    const bool write_back = (rows == nullptr) && (dp != nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = hp[i];
+        if (dp) v += to_f32<TA>(dp[i]);
+        if (write_back) hp[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    TA* op = out + (size_t)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = hp[i];
+        if (dp && !write_back) v += to_f32<TA>(dp[i]);
+        op[i] = from_f32<TA>(v * inv * to_f32<TW>(w[i]));
+    }
+}
+
+RI_API int ri_add_rmsnorm(float* h, const void* delta, const void* w, int w_dtype, float eps,
+                          void* out, int act_dtype, const int* rows, int n_rows, int d,
+                          void* stream) {
+    if (n_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+#define RI_LAUNCH(TA, TW)                                                                  \
+    add_rmsnorm_kernel<TA, TW><<<n_rows, threads, 0, s>>>(h, (const TA*)delta, (const TW*)w, \
+                                                          eps, (TA*)out, rows, d)
+    if (act_dtype == RI_BF16) {
+        if (w_dtype == RI_BF16) RI_LAUNCH(bf16, bf16); else RI_LAUNCH(bf16, float);
+    } else {
+        if (w_dtype == RI_BF16) RI_LAUNCH(float, bf16); else RI_LAUNCH(float, float);
+    }
+#undef RI_LAUNCH
+    return ri_launch_status();
+}
+
+// h += delta on every row (flush of the last pending residual when the stream itself is wanted)
+template <typename TA>
+__global__ void residual_add_kernel(float* __restrict__ h, const TA* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) h[i] += to_f32<TA>(delta[i]);
+}
+
+RI_API int ri_residual_add(float* h, const void* delta, int act_dtype, long long n, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (act_dtype == RI_BF16) residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(h, (const bf16*)delta, (size_t)n);
+    else residual_add_kernel<float><<<blocks, 256, 0, s>>>(h, (const float*)delta, (size_t)n);
+    return ri_launch_status();
+}
+
+// --------------------------------------------------- RoPE + write of K,V into pages
+// qkv row t: [Hq heads of q | Hkv heads of k | Hkv heads of v], head_dim each.
+// q is rotated in place; k is rotated and written to the page slot of token t; v is
+// copied there.  The pair of element i is i + rotary_dim/2; elements at and beyond
+// rotary_dim pass through.  cos/sin tables are fp32 [positions, rotary_dim/2].
+// Cache layout of one layer: [page][K|V][kv head][slot in page][head_dim].
+template <typename TA>
+__global__ void rope_scatter_kernel(TA* __restrict__ qkv, int row_stride,
+                                    const int* __restrict__ positions,
+                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                    const int* __restrict__ slot_of_token, TA* __restrict__ cache,
+                                    int Hq, int Hkv, int hd, int rot, int page_size) {
+    const int t = blockIdx.x;
+    const int half = rot >> 1;
+    const int pos = positions[t];
+    TA* row = qkv + (size_t)t * row_stride;
+    const float* ct = cos_t + (size_t)pos * half;
+    const float* st = sin_t + (size_t)pos * half;
+    const int slot = (slot_of_token && Hkv > 0) ? slot_of_token[t] : -1;
+    TA* kdst = nullptr;
+    TA* vdst = nullptr;
+    if (slot >= 0) {
+        const int page = slot / page_size, off = slot - page * page_size;
+        kdst = cache + ((size_t)(page * 2 + 0) * Hkv * page_size + off) * hd;
+        vdst = cache + ((size_t)(page * 2 + 1) * Hkv * page_size + off) * hd;
+    }
+    const size_t head_step = (size_t)page_size * hd;    // between kv heads inside a page
+    const int n_rot = (Hq + Hkv) * half;
+    for (int wi = threadIdx.x; wi < n_rot; wi += blockDim.x) {
+        const int head = wi / half, i = wi - head * half;
+        TA* p = row + (size_t)head * hd;
+        const float x1 = to_f32<TA>(p[i]), x2 = to_f32<TA>(p[i + half]);
+        const float c = ct[i], s = st[i];
+        const TA y1 = from_f32<TA>(x1 * c - x2 * s);
+        const TA y2 = from_f32<TA>(x1 * s + x2 * c);
+        if (head < Hq) {
+            p[i] = y1;
+            p[i + half] = y2;
+        } else if (kdst) {
+            TA* kd = kdst + (size_t)(head - Hq) * head_step;
+            kd[i] = y1;
+            kd[i + half] = y2;
+        }
+    }
+    if (kdst) {
+        const int pass = hd - rot;                      // unrotated tail of each k head
+        for (int wi = threadIdx.x; wi < Hkv * pass; wi += blockDim.x) {
+            const int g = wi / pass, i = rot + (wi - g * pass);
+            kdst[(size_t)g * head_step + i] = row[(size_t)(Hq + g) * hd + i];
+        }
+        const TA* vsrc = row + (size_t)(Hq + Hkv) * hd;
+        for (int wi = threadIdx.x; wi < Hkv * hd; wi += blockDim.x) {
+            const int g = wi / hd, i = wi - g * hd;
+            vdst[(size_t)g * head_step + i] = vsrc[wi];
+        }
+    }
+}
+
+RI_API int ri_rope_scatter(void* qkv, int act_dtype, int row_stride, const int* positions,
+                           const float* cos_t, const float* sin_t, const int* slot_of_token,
+                           void* cache, int tokens, int Hq, int Hkv, int hd, int rot,
+                           int page_size, void* stream) {
+    if (tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int work = (Hq + 2 * Hkv) * hd / 2;
+    const int threads = work >= 1024 ? 256 : 128;
+    if (act_dtype == RI_BF16)
+        rope_scatter_kernel<bf16><<<tokens, threads, 0, s>>>((bf16*)qkv, row_stride, positions, cos_t,
+            sin_t, slot_of_token, (bf16*)cache, Hq, Hkv, hd, rot, page_size);
+    else
+        rope_scatter_kernel<float><<<tokens, threads, 0, s>>>((float*)qkv, row_stride, positions, cos_t,
+            sin_t, slot_of_token, (float*)cache, Hq, Hkv, hd, rot, page_size);
+    return ri_launch_status();
+}
+
+// ------------------------------------------------------------------ SiLU(gate) * up
+// gu row: [gate (I) | up (I)]; out[t, j] = gate / (1 + e^-gate) * up.
+template <typename TA>
+__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter) {
+    const int t = blockIdx.y;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= inter) return;
+    const TA* row = gu + (size_t)t * 2 * inter;
+    const float g = to_f32<TA>(row[j]), u = to_f32<TA>(row[inter + j]);
+    out[(size_t)t * inter + j] = from_f32<TA>(g / (1.0f + expf(-g)) * u);
+}
+
+RI_API int ri_silu_mul(const void* gu, void* out, int act_dtype, int tokens, int inter, void* stream) {
+    if (tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((inter + 255) / 256, tokens);
+    if (act_dtype == RI_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)gu, (bf16*)out, inter);
+    else silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gu, (float*)out, inter);
+    return ri_launch_status();
+}

@@ -1,0 +1,190 @@
+// Choosing the next token on the device: greedy argmax, and temperature sampling with
+// top-k, min-p and top-p filters.
+//
+// Greedy follows crates/infer-backend-cuda/src/kernels/sampler/sampler.cu:66-105 (the
+// lowest index wins ties).  The filtered draw follows RustInfer's host sampler
+// (crates/infer-worker/src/application/sampler_stack.rs:242-351): logit/T, sort
+// descending, top-k, exp(x - max), min-p, normalise, top-p (keep until the cumulative
+// share reaches p, at least one), then walk the cumulative weights with draw * total.
+// The reference copies the logits to the host for this; here one CTA per row sorts the
+// row in a scratch buffer on the device (bitonic, 64-bit keys made of the logit and the
+// token id, so equal logits are ordered by ascending id) and does the sums in fp64, in
+// rank order within each thread's contiguous segment.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ unsigned int ordered_bits(float v) {
+    if (v != v) v = -INFINITY;                           // NaN sorts last
+    unsigned int u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float from_ordered(unsigned int k) {
+    unsigned int u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(u);
+}
+
+// ------------------------------------------------------------------------- argmax
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
+    __shared__ unsigned long long best[32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    unsigned long long mine = 0ull;                      // (ordered logit << 32) | ~index
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const unsigned long long key =
+            ((unsigned long long)ordered_bits(row[i]) << 32) | (unsigned int)(0xffffffffu - (unsigned int)i);
+        mine = key > mine ? key : mine;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
+        mine = other > mine ? other : mine;
+    }
+    if ((threadIdx.x & 31) == 0) best[threadIdx.x >> 5] = mine;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        mine = threadIdx.x < ((blockDim.x + 31) >> 5) ? best[threadIdx.x] : 0ull;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
+            mine = other > mine ? other : mine;
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xffffffffu - (unsigned int)(mine & 0xffffffffu));
+    }
+}
+
+// ---------------------------------------------------------------- filtered sampling
+constexpr int ST = 1024;
+
+__device__ __forceinline__ double weight_of(unsigned long long key, float top, double inv_t) {
+    const float v = from_ordered((unsigned int)(key >> 32));
+    if (v == -INFINITY) return 0.0;
+    return exp(((double)v - (double)top) * inv_t);
+}
+
+// Exclusive scan of one double per thread in thread order; returns this thread's prefix,
+// *total gets the sum.  Serial over 1024 values: the order of additions is fixed.
+__device__ double exclusive_scan(double v, double* buf, double* total) {
+    __syncthreads();
+    buf[threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double run = 0.0;
+        for (int i = 0; i < ST; ++i) { const double t = buf[i]; buf[i] = run; run += t; }
+        buf[ST] = run;
+    }
+    __syncthreads();
+    *total = buf[ST];
+    return buf[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(ST)
+sample_kernel(const float* __restrict__ logits, int ld, int vocab, int vpad,
+              unsigned long long* __restrict__ scratch, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const float* __restrict__ min_p, const double* __restrict__ draw,
+              int* __restrict__ out) {
+    __shared__ double buf[ST + 1];
+    __shared__ int found;
+    const int r = blockIdx.x, tid = threadIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    unsigned long long* s = scratch + (size_t)r * vpad;
+
+    for (int i = tid; i < vpad; i += ST)
+        s[i] = i < vocab ? (((unsigned long long)ordered_bits(row[i]) << 32) |
+                            (unsigned int)(0xffffffffu - (unsigned int)i)) : 0ull;
+    __syncthreads();
+    for (int k = 2; k <= vpad; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = tid; i < vpad; i += ST) {
+                const int p = i ^ j;
+                if (p > i) {
+                    const unsigned long long a = s[i], b = s[p];
+                    const bool desc = (i & k) == 0;
+                    if (desc ? a < b : a > b) { s[i] = b; s[p] = a; }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    const float temp = temperature[r];
+    const int tk = top_k[r];
+    const float tp = top_p[r], mp = min_p[r];
+    if (!(temp > 0.f) || tk == 1 || !(tp > 0.f)) {       // greedy
+        if (tid == 0) out[r] = (int)(0xffffffffu - (unsigned int)(s[0] & 0xffffffffu));
+        return;
+    }
+    const double inv_t = 1.0 / (double)temp;
+    const float top = from_ordered((unsigned int)(s[0] >> 32));
+    int n = vocab;
+    if (tk > 0 && tk < n) n = tk;
+    int seg = (n + ST - 1) / ST;
+    int lo = min(tid * seg, n), hi = min(lo + seg, n);
+
+    // min-p: weights fall with rank, so the kept set is a prefix
+    if (mp > 0.f) {
+        if (tid == 0) found = n;
+        __syncthreads();
+        const double thr = (double)mp;                   // the largest weight is exp(0) = 1
+        for (int i = lo; i < hi; ++i)
+            if (weight_of(s[i], top, inv_t) < thr) { atomicMin(&found, i); break; }
+        __syncthreads();
+        n = max(found, 1);
+        __syncthreads();
+        seg = (n + ST - 1) / ST;
+        lo = min(tid * seg, n); hi = min(lo + seg, n);
+    }
+    double part = 0.0, total = 0.0;
+    for (int i = lo; i < hi; ++i) part += weight_of(s[i], top, inv_t);
+    double prefix = exclusive_scan(part, buf, &total);
+
+    if (tp < 1.f) {                                      // top-p
+        if (tid == 0) found = n;
+        __syncthreads();
+        double cum = prefix;
+        for (int i = lo; i < hi; ++i) {
+            cum += weight_of(s[i], top, inv_t);
+            if (cum / total >= (double)tp) { atomicMin(&found, i + 1); break; }
+        }
+        __syncthreads();
+        n = max(found, 1);
+        __syncthreads();
+        seg = (n + ST - 1) / ST;
+        lo = min(tid * seg, n); hi = min(lo + seg, n);
+        part = 0.0;
+        for (int i = lo; i < hi; ++i) part += weight_of(s[i], top, inv_t);
+        prefix = exclusive_scan(part, buf, &total);
+    }
+    double u = draw[r];
+    u = u < 0.0 ? 0.0 : (u > 1.0 - 2.220446049250313e-16 ? 1.0 - 2.220446049250313e-16 : u);
+    const double target = u * total;
+    if (tid == 0) found = n - 1;
+    __syncthreads();
+    double cum = prefix;
+    for (int i = lo; i < hi; ++i) {
+        cum += weight_of(s[i], top, inv_t);
+        if (target < cum) { atomicMin(&found, i); break; }
+    }
+    __syncthreads();
+    if (tid == 0) out[r] = (int)(0xffffffffu - (unsigned int)(s[found] & 0xffffffffu));
+}
+}  // namespace
+
+RI_API int ri_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* stream) {
+    if (rows <= 0) return 0;
+    const int threads = vocab >= 4096 ? 1024 : 256;
+    argmax_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
+    return ri_launch_status();
+}
+
+// scratch: rows * vpad 64-bit words, vpad = vocab rounded up to a power of two.
+RI_API int ri_sample(const float* logits, int ld, int rows, int vocab, int vpad,
+                     unsigned long long* scratch, const float* temperature, const int* top_k,
+                     const float* top_p, const float* min_p, const double* draw, int* out,
+                     void* stream) {
+    if (rows <= 0) return 0;
+    if (vpad < vocab || (vpad & (vpad - 1)) != 0) return (int)cudaErrorInvalidValue;
+    sample_kernel<<<rows, ST, 0, (cudaStream_t)stream>>>(logits, ld, vocab, vpad, scratch, temperature,
+                                                         top_k, top_p, min_p, draw, out);
+    return ri_launch_status();
+}

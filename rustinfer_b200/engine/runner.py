@@ -1,0 +1,280 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes entries that may be whole prompts, portions of prompts cut anywhere, and
+single decoded tokens, side by side.  It runs exactly the tokens it is given, as one
+ragged batch, over what earlier steps left in the cache, and returns fp32 logits at the
+wanted places.  Generation, the scheduler and trace replay all go through this one
+function.
+
+RustInfer's counterpart is `Runtime::step` over a `StepRequest`
+(crates/infer-worker/src/application/runtime/mod.rs:561-593) with the plan built by
+`build_plan` (crates/infer-worker/src/application/runtime/plan.rs:24-154); it returns
+sampled tokens, where this returns logits and leaves sampling to the caller.  The checks
+before launch are the ones the reference's plan builder makes (:42-105): nothing is
+launched with an index the kernels could not follow.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheLayout, CacheManager
+from ..cache.pages import OutOfPages
+from ..config.registry import load_model_description
+from ..models.decoder import Decoder
+from ..parts.base import (BuildContext, FixedState, GroupStep, HostEntry, PagedKV, PagedLayerCache,
+                          StateLayerCache, StepContext)
+from ..weights.loader import load_weights
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+                 "float32": torch.float32, "fp32": torch.float32}
+_STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
+
+
+class StepError(ValueError):
+    """The batch handed to `step` cannot be run as given."""
+
+
+@dataclass
+class StepEntry:
+    request_id: Any
+    tokens: Sequence[int]
+    want: Sequence[int] = ()            # places among `tokens` whose logits are returned
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        return name
+    try:
+        return _TORCH_DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"dtype {name!r}: choose bfloat16 or float32")
+
+
+class _Staging:
+    """A ring of pinned host buffers and the device buffer each step's index arrays are
+    copied into with one transfer."""
+
+    def __init__(self, n_ints: int, device: torch.device, depth: int = 3):
+        self.host = [torch.empty(n_ints, dtype=torch.int32).pin_memory() for _ in range(depth)]
+        self.events: List[Optional[torch.cuda.Event]] = [None] * depth
+        self.dev = torch.empty(n_ints, dtype=torch.int32, device=device)
+        self.turn = 0
+
+    def next_host(self) -> Tuple[int, torch.Tensor]:
+        i = self.turn
+        self.turn = (self.turn + 1) % len(self.host)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        return i, self.host[i]
+
+    def upload(self, i: int, n: int) -> None:
+        self.dev[:n].copy_(self.host[i][:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class ModelRunner:
+    """Model, cache and step function of one model folder on one GPU."""
+
+    def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", max_model_len: int = 4096,
+                 page_size: int = 16, num_pages: Optional[int] = None, max_batch_seqs: int = 64,
+                 max_batch_tokens: int = 8192):
+        if not torch.cuda.is_available():
+            raise RuntimeError("rustinfer_b200 runs on a CUDA device (sm_100a) only; there is no CPU path")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.dtype = parse_dtype(dtype)
+        # the 32-bit path is true fp32 everywhere: no TF32 in any library product either
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+        self.family, self.config, self.spec = load_model_description(model_dir)
+        self.max_model_len = int(max_model_len)
+        self.page_size = int(page_size)
+        self.max_batch_seqs = int(max_batch_seqs)
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.model = Decoder(self.spec)
+        self.ctx = BuildContext(self.device, self.dtype, self.max_model_len, self.page_size)
+        self.model.prepare(self.ctx)
+        self.model.load(load_weights(model_dir, self.model.param_decls(), self.dtype, self.device))
+
+        self.layout = CacheLayout.from_needs(self.model.cache_needs())
+        self.max_pages_per_request = (self.max_model_len + self.page_size - 1) // self.page_size
+        if num_pages is None:
+            num_pages = self.max_batch_seqs * self.max_pages_per_request
+        self.num_pages = int(num_pages)
+        paged = self.layout.paged_groups()
+        self.cache = CacheManager(self.layout, [self.num_pages] * len(paged), self.page_size,
+                                  self.max_batch_seqs)
+        self._alloc_storage()
+        self.tile_rows = self.model.attention_tile_rows()
+        cap_t, cap_b = self.max_batch_tokens, self.max_batch_seqs
+        n_ints = 4 * cap_t + 4 * cap_b + 64
+        n_ints += len(paged) * (cap_b * self.max_pages_per_request + cap_t + 16)
+        for r in self.tile_rows:
+            n_ints += 2 * (cap_t // r + cap_b + 8)
+        self._staging = _Staging(n_ints, self.device)
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------------ storage
+    def _alloc_storage(self) -> None:
+        self.group_storage: List[torch.Tensor] = []
+        self._paged_index: Dict[int, int] = {}
+        for gi, g in enumerate(self.layout.groups):
+            n = len(g.entries)
+            if isinstance(g.need, PagedKV):
+                self._paged_index[gi] = len(self._paged_index)
+                t = torch.zeros((n, self.num_pages, 2, g.need.num_kv_heads, self.page_size, g.need.head_dim),
+                                dtype=self.dtype, device=self.device)
+            elif isinstance(g.need, FixedState):
+                t = torch.zeros((n, self.max_batch_seqs) + tuple(g.need.shape),
+                                dtype=_STATE_DTYPES[g.need.dtype], device=self.device)
+            else:
+                raise TypeError(f"unknown cache need {g.need!r}")
+            self.group_storage.append(t)
+        self.entry_caches: List[Any] = []
+        for i, loc in enumerate(self.layout.entry_cache):
+            if loc is None:
+                self.entry_caches.append(None)
+                continue
+            gi, idx = loc
+            if isinstance(self.layout.groups[gi].need, PagedKV):
+                self.entry_caches.append(PagedLayerCache(self.group_storage[gi][idx], self._paged_index[gi],
+                                                         self.layout.entry_writes[i]))
+            else:
+                self.entry_caches.append(StateLayerCache(self.group_storage[gi][idx]))
+
+    def cache_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.group_storage)
+
+    # ----------------------------------------------------------------------- requests
+    def open(self, request_id: Any) -> None:
+        self.cache.open(request_id)
+
+    def close(self, request_id: Any) -> None:
+        self.cache.close(request_id)
+
+    # --------------------------------------------------------------------------- plan
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        if len(entries) > self.max_batch_seqs:
+            raise StepError(f"{len(entries)} entries exceed max_batch_seqs {self.max_batch_seqs}")
+        seen = set()
+        total = 0
+        vocab = self.spec.vocab_size
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if not self.cache.is_open(e.request_id):
+                raise StepError(f"request {e.request_id!r} is not open")
+            q = len(e.tokens)
+            if q < 1:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            total += q
+            if self.cache.length(e.request_id) + q > self.max_model_len:
+                raise StepError(f"request {e.request_id!r} would reach {self.cache.length(e.request_id) + q} "
+                                f"tokens, max_model_len is {self.max_model_len}")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise StepError(f"request {e.request_id!r}: token id {t} outside [0, {vocab})")
+            for w in e.want:
+                if not 0 <= int(w) < q:
+                    raise StepError(f"request {e.request_id!r}: wanted place {w} outside its {q} tokens")
+        if total > self.max_batch_tokens:
+            raise StepError(f"{total} tokens exceed max_batch_tokens {self.max_batch_tokens}")
+
+    def _build(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, Optional[torch.Tensor]]:
+        ps = self.page_size
+        B = len(entries)
+        q_lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=B)
+        pos0 = np.fromiter((self.cache.length(e.request_id) for e in entries), dtype=np.int64, count=B)
+        cu_q = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(q_lens, out=cu_q[1:])
+        T = int(cu_q[-1])
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        entry_of_token = np.repeat(np.arange(B), q_lens)
+        positions = np.arange(T) - cu_q[entry_of_token] + pos0[entry_of_token]
+        kv_len = pos0 + q_lens
+        slots = np.fromiter((self.cache.slot(e.request_id) for e in entries), dtype=np.int64, count=B)
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            rows.extend(int(cu_q[i]) + int(w) for w in e.want)
+
+        sections: List[np.ndarray] = [token_ids, positions, cu_q, kv_len, slots,
+                                      np.asarray(rows, dtype=np.int64)]
+        max_blocks = int(((kv_len + ps - 1) // ps).max())
+        for gi in self.layout.paged_groups():
+            table = np.zeros((B, max_blocks), dtype=np.int64)
+            for i, e in enumerate(entries):
+                t = self.cache.block_table(e.request_id, gi)
+                n = min(len(t), max_blocks)
+                table[i, :n] = t[:n]
+            page_of_token = table[entry_of_token, positions // ps]
+            if (page_of_token < 0).any():
+                raise StepError("a token would be written to a page that was given back")
+            slot_of_token = page_of_token * ps + positions % ps
+            np.maximum(table, 0, out=table)
+            sections += [table.reshape(-1), slot_of_token]
+        for r in self.tile_rows:
+            n_tiles = (q_lens + r - 1) // r
+            tile_entry = np.repeat(np.arange(B), n_tiles)
+            first = np.zeros(B, dtype=np.int64)
+            np.cumsum(n_tiles[:-1], out=first[1:])
+            tile_q0 = (np.arange(int(n_tiles.sum())) - first[tile_entry]) * r
+            sections += [tile_entry, tile_q0]
+
+        idx, host = self._staging.next_host()
+        offsets: List[Tuple[int, int]] = []
+        at = 0
+        hv = host.numpy()
+        for s in sections:
+            n = s.size
+            hv[at: at + n] = s
+            offsets.append((at, n))
+            at += (n + 3) & ~3                      # every section starts on a 16-byte boundary
+        self._staging.upload(idx, at)
+        dev = self._staging.dev
+        views = [dev[o: o + n] for o, n in offsets]
+        it = iter(views[6:])
+        groups = []
+        for _ in self.layout.paged_groups():
+            table = next(it).view(B, max_blocks)
+            groups.append(GroupStep(table, next(it)))
+        tiles = {r: (next(it), next(it)) for r in self.tile_rows}
+        host_entries = [HostEntry(e.request_id, int(slots[i]), int(q_lens[i]), int(pos0[i]))
+                        for i, e in enumerate(entries)]
+        step = StepContext(
+            num_tokens=T, num_entries=B, token_ids=views[0], positions=views[1], cu_q=views[2],
+            kv_len=views[3], state_slots=views[4], groups=groups, tiles=tiles, entries=host_entries,
+            max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), decode_only=bool((q_lens == 1).all()))
+        return step, (views[5] if rows else None)
+
+    # --------------------------------------------------------------------------- step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch.  Returns fp32 logits [wanted, vocab] on the device in the order of
+        the entries and of their `want`, or None when nothing is wanted.  Raises `OutOfPages`
+        before anything runs if the cache cannot hold the new tokens (nothing is changed)."""
+        self._validate(entries)
+        self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
+        self._zero_new_state()
+        step, rows = self._build(entries)
+        logits = self.model.forward(step, self.entry_caches, rows)
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def _zero_new_state(self) -> None:
+        new = self.cache.newly_opened_slots
+        if not new:
+            return
+        for gi, g in enumerate(self.layout.groups):
+            if isinstance(g.need, FixedState):
+                self.group_storage[gi][:, new] = 0
+        new.clear()

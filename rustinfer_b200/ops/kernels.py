@@ -1,0 +1,170 @@
+"""Typed Python fronts of the CUDA kernels.  Each checks what the kernel assumes
+(device, dtype, layout, sizes) and raises instead of computing something wrong."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import library as L
+from .library import KernelError, check, dtype_code, require_cuda, stream_ptr
+
+
+def _p(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _contig(t: torch.Tensor, name: str) -> None:
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, got {t.dtype}")
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t,:] (fp32) = table[ids[t],:]."""
+    require_cuda(ids, table, out)
+    _i32(ids, "ids"); _contig(table, "table"); _contig(out, "out")
+    if out.dtype != torch.float32 or out.shape != (ids.numel(), table.shape[1]):
+        raise KernelError(f"embed_gather: out must be fp32 [{ids.numel()}, {table.shape[1]}]")
+    check(L.core().ri_embed_gather(_p(ids), _p(table), dtype_code(table.dtype), _p(out),
+                                   ids.numel(), table.shape[1], table.shape[0], stream_ptr()),
+          "embed_gather")
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """h (fp32 [T,d]) += delta; out = rmsnorm(h) * weight in out's dtype.  With `rows`
+    (int32 [R]) only those rows are normed into out [R,d] and h is left as it is."""
+    require_cuda(h, delta, weight, out, rows)
+    d = h.shape[-1]
+    _contig(h, "h"); _contig(out, "out"); _contig(weight, "weight"); _i32(rows, "rows")
+    if h.dtype != torch.float32:
+        raise KernelError("add_rmsnorm: the residual stream is fp32")
+    if weight.numel() != d:
+        raise KernelError(f"add_rmsnorm: weight has {weight.numel()} elements, rows have {d}")
+    n_rows = h.shape[0] if rows is None else rows.numel()
+    if out.shape != (n_rows, d):
+        raise KernelError(f"add_rmsnorm: out must be [{n_rows}, {d}], got {tuple(out.shape)}")
+    if delta is not None:
+        _contig(delta, "delta")
+        if delta.shape != h.shape or delta.dtype != out.dtype:
+            raise KernelError("add_rmsnorm: delta must match h's shape and out's dtype")
+    check(L.core().ri_add_rmsnorm(_p(h), _p(delta), _p(weight), dtype_code(weight.dtype), float(eps),
+                                  _p(out), dtype_code(out.dtype), _p(rows), n_rows, d, stream_ptr()),
+          "add_rmsnorm")
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
+    require_cuda(h, delta)
+    _contig(h, "h"); _contig(delta, "delta")
+    if h.dtype != torch.float32 or h.shape != delta.shape:
+        raise KernelError("residual_add: h is fp32 and delta has its shape")
+    check(L.core().ri_residual_add(_p(h), _p(delta), dtype_code(delta.dtype), h.numel(), stream_ptr()),
+          "residual_add")
+
+
+def rope_scatter(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                 slot_of_token: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                 num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int) -> None:
+    """Rotate q (in place) and k of qkv [T, (Hq+2Hkv)*hd]; write k,v of token t into the
+    cache [pages, 2, Hkv, page, hd] at slot_of_token[t] (page*page_size + offset; <0 skips)."""
+    require_cuda(qkv, positions, cos, sin, slot_of_token, cache)
+    _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token")
+    T = qkv.shape[0]
+    if qkv.stride(1) != 1 or qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError("rope_scatter: qkv must be [T, (Hq+2Hkv)*head_dim] with unit column stride")
+    if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
+        raise KernelError(f"rope_scatter: rotary_dim {rotary_dim} must be even and at most head_dim")
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape[1] != rotary_dim // 2:
+        raise KernelError("rope_scatter: cos/sin are fp32 [positions, rotary_dim/2]")
+    page = 0
+    if cache is not None:
+        _contig(cache, "cache")
+        if cache.dtype != qkv.dtype or cache.dim() != 5 or cache.shape[1] != 2 or \
+                cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+            raise KernelError("rope_scatter: cache must be [pages, 2, Hkv, page, head_dim] of qkv's dtype")
+        page = cache.shape[3]
+    check(L.core().ri_rope_scatter(_p(qkv), dtype_code(qkv.dtype), qkv.stride(0), _p(positions),
+                                   _p(cos), _p(sin), _p(slot_of_token), _p(cache), T, num_heads,
+                                   num_kv_heads if cache is not None else 0, head_dim, rotary_dim,
+                                   max(page, 1), stream_ptr()), "rope_scatter")
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor) -> None:
+    require_cuda(gu, out)
+    _contig(gu, "gu"); _contig(out, "out")
+    T, two_i = gu.shape
+    if two_i % 2 or out.shape != (T, two_i // 2) or out.dtype != gu.dtype:
+        raise KernelError("silu_mul: gu is [T, 2I], out [T, I] of the same dtype")
+    check(L.core().ri_silu_mul(_p(gu), _p(out), dtype_code(gu.dtype), T, two_i // 2, stream_ptr()),
+          "silu_mul")
+
+
+def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T, exact fp32."""
+    require_cuda(a, w, out)
+    for t, n in ((a, "a"), (w, "w"), (out, "out")):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"gemm_f32: {n} must be a 2-d fp32 tensor with unit column stride")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm_f32: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    check(L.core().ri_gemm_f32(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0),
+                               M, N, K, stream_ptr()), "gemm_f32")
+
+
+def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                    cu_q: torch.Tensor, kv_len: torch.Tensor, tile_entry: torch.Tensor,
+                    tile_q0: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                    scale: float, window: Optional[int]) -> None:
+    """q [T, >=Hq*hd] (may be a column view of the qkv buffer), out [T, Hq*hd]."""
+    require_cuda(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_q0)
+    for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len"),
+                 (tile_entry, "tile_entry"), (tile_q0, "tile_q0")):
+        _i32(t, n)
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.dtype != cache.dtype or out.dtype != cache.dtype:
+        raise KernelError("attention: q, out and cache share a dtype; q and out have unit column stride")
+    _contig(cache, "cache")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError("attention: cache must be [pages, 2, Hkv, page, head_dim]")
+    if num_heads % num_kv_heads:
+        raise KernelError("attention: heads must be a multiple of kv heads")
+    lib = L.attention_plain(head_dim)
+    check(lib.ri_attention_plain(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache),
+                                 dtype_code(cache.dtype), _p(block_table), block_table.stride(0),
+                                 _p(cu_q), _p(kv_len), _p(tile_entry), _p(tile_q0), tile_entry.numel(),
+                                 num_heads, num_kv_heads, cache.shape[3], float(scale),
+                                 int(window) if window else 0, stream_ptr()), "attention_plain")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    require_cuda(logits, out)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32:
+        raise KernelError("argmax: logits fp32 [R,V], out int32 [R]")
+    check(L.core().ri_argmax(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out),
+                             stream_ptr()), "argmax")
+
+
+def sample(logits: torch.Tensor, scratch: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, min_p: torch.Tensor, draw: torch.Tensor, out: torch.Tensor) -> None:
+    require_cuda(logits, scratch, temperature, top_k, top_p, min_p, draw, out)
+    R, V = logits.shape
+    vpad = 1 << max(1, (V - 1).bit_length())
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits fp32 [R,V]")
+    if scratch.dtype != torch.int64 or scratch.numel() < R * vpad:
+        raise KernelError(f"sample: scratch must hold {R * vpad} int64")
+    if (temperature.dtype, top_k.dtype, top_p.dtype, min_p.dtype, draw.dtype, out.dtype) != \
+            (torch.float32, torch.int32, torch.float32, torch.float32, torch.float64, torch.int32):
+        raise KernelError("sample: parameter dtypes")
+    check(L.core().ri_sample(_p(logits), logits.stride(0), R, V, vpad, _p(scratch), _p(temperature),
+                             _p(top_k), _p(top_p), _p(min_p), _p(draw), _p(out), stream_ptr()), "sample")
+
+
+def sample_scratch_elems(rows: int, vocab: int) -> int:
+    return rows * (1 << max(1, (vocab - 1).bit_length()))

@@ -1,0 +1,92 @@
+"""Loading the compiled kernels through ctypes and calling them on torch tensors.
+
+The libraries export plain C functions that take device pointers, sizes and a stream.
+There is no other implementation behind these wrappers: a missing library is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+
+from . import build
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int
+_L = ctypes.c_longlong
+_F = ctypes.c_float
+
+_SIGNATURES = {
+    "ri_embed_gather": [_P, _P, _I, _P, _I, _I, _I, _P],
+    "ri_add_rmsnorm": [_P, _P, _P, _I, _F, _P, _I, _P, _I, _I, _P],
+    "ri_residual_add": [_P, _P, _I, _L, _P],
+    "ri_rope_scatter": [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "ri_silu_mul": [_P, _P, _I, _I, _I, _P],
+    "ri_gemm_f32": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
+    "ri_argmax": [_P, _I, _I, _I, _P, _P],
+    "ri_sample": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
+    "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+}
+
+_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "sampling.cu"]
+_loaded: Dict[str, ctypes.CDLL] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
+    for name, args in _SIGNATURES.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _I
+    return lib
+
+
+def _load(name: str, sources, defines=()) -> ctypes.CDLL:
+    lib = _loaded.get(name)
+    if lib is None:
+        path = build.build_library(name, sources, defines)
+        lib = _bind(ctypes.CDLL(path))
+        _loaded[name] = lib
+    return lib
+
+
+def core() -> ctypes.CDLL:
+    return _load("ri_core", _CORE_SOURCES)
+
+
+def attention_plain(head_dim: int) -> ctypes.CDLL:
+    if head_dim % 16 != 0 or not 16 <= head_dim <= 512:
+        raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to 512, "
+                          f"got {head_dim}")
+    return _load(f"ri_attention_plain_hd{head_dim}", ["attention_plain.cu"], [f"RI_HEAD_DIM={head_dim}"])
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        lib = core()
+        lib.ri_error_string.restype = ctypes.c_char_p
+        lib.ri_error_string.argtypes = [_I]
+        raise KernelError(f"{what}: CUDA error {code} ({lib.ri_error_string(code).decode()})")
+
+
+def require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the sm_100a kernels take CUDA tensors only; there is no CPU path")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")

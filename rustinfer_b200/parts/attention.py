@@ -1,0 +1,99 @@
+"""Grouped-query attention over the paged cache
+(crates/infer-worker/src/components/attention.rs:21-37,83-179): fused q,k,v projection,
+rotary encoding of q and k, write of k and v into the request's pages, attention of every
+new token over the keys it may see, output projection.  The residual add and the norm
+before it belong to the block, not to this part.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..ops import kernels as K
+from .base import (BuildContext, Mixer, PagedKV, PagedLayerCache, ParamDecl, POSITIONS, StepContext,
+                   register_mixer)
+from .linear import Linear
+from .spec import PartSpec
+
+
+@register_mixer("gqa_attention")
+class GQAAttention(Mixer):
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, scale, window (None: all keys),
+    position (PartSpec of a rotary encoding, or None), own_kv (False: the layer projects no
+    keys or values and reads the cache another layer wrote)."""
+
+    graph_safe = True
+    attention_tile_rows = (16,)
+
+    def __init__(self, params):
+        super().__init__(params)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.Hq, self.Hkv, self.hd = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        self.scale = float(p["scale"])
+        self.window = int(p["window"]) if p.get("window") else None
+        self.own_kv = bool(p.get("own_kv", True))
+        if self.Hq % self.Hkv:
+            raise ValueError(f"{self.Hq} heads are not a multiple of {self.Hkv} kv heads")
+        if self.hd % 16 or not 16 <= self.hd <= 512:
+            raise ValueError(f"head_dim {self.hd}: the attention kernels take multiples of 16 up to 512")
+        pos = p.get("position")
+        self.position_spec: Optional[PartSpec] = pos
+        self.position = None
+        self.qkv: Optional[Linear] = None
+        self.o: Optional[Linear] = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        q, kv = self.Hq * self.hd, self.Hkv * self.hd
+        d = {"q_proj.weight": ParamDecl((q, self.hidden)),
+             "o_proj.weight": ParamDecl((self.hidden, q))}
+        if self.own_kv:
+            d["k_proj.weight"] = ParamDecl((kv, self.hidden))
+            d["v_proj.weight"] = ParamDecl((kv, self.hidden))
+        return d
+
+    def cache_need(self):
+        return PagedKV(self.Hkv, self.hd, self.window)
+
+    def prepare(self, ctx: BuildContext) -> None:
+        super().prepare(ctx)
+        if self.position_spec is not None:
+            key = ("position", self.position_spec.key(), ctx.max_model_len)
+            if key not in ctx.shared:
+                part = POSITIONS.build(self.position_spec)
+                part.prepare(ctx)
+                ctx.shared[key] = part
+            self.position = ctx.shared[key]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        # q, k, v fused by rows into one matrix, gate rows first
+        # (crates/infer-worker/src/models/loader.rs:419-454)
+        parts = [tensors["q_proj.weight"]]
+        if self.own_kv:
+            parts += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        dt = torch.float32 if any(t.dtype == torch.float32 for t in parts) else parts[0].dtype
+        self.qkv = Linear(torch.cat([t.to(dt) for t in parts], dim=0))
+        self.o = Linear(tensors["o_proj.weight"])
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache) -> torch.Tensor:
+        T = x.shape[0]
+        g = step.groups[cache.group]
+        qkv = self.qkv(x, out_dtype=self.ctx.dtype)
+        writes = self.own_kv and cache.writes
+        if self.position is not None:
+            K.rope_scatter(qkv if writes else self._q_only(qkv), step.positions, self.position.cos,
+                           self.position.sin, g.slot_of_token if writes else None,
+                           cache.kv if writes else None, self.Hq, self.Hkv if writes else 0, self.hd,
+                           self.position.rotary_dim)
+        else:
+            raise NotImplementedError("attention without a rotary encoding has no cache-write kernel yet")
+        q = qkv[:, : self.Hq * self.hd]
+        out = torch.empty((T, self.Hq * self.hd), dtype=self.ctx.dtype, device=x.device)
+        tile_entry, tile_q0 = step.tiles[16]
+        K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
+                          self.Hq, self.Hkv, self.hd, self.scale, self.window)
+        return self.o(out, out_dtype=self.ctx.dtype)
+
+    def _q_only(self, qkv: torch.Tensor) -> torch.Tensor:
+        return qkv[:, : self.Hq * self.hd]

@@ -1,0 +1,66 @@
+"""How a layer's parts are arranged.  "pre_norm": the stream h is only ever changed by
+adding what a sublayer returned, and that add is fused into the next norm:
+
+    x = mixer_norm(h += pending);  pending = mixer(x)
+    x = ffn_norm(h += pending);    pending = ffn(x)
+
+(crates/infer-worker/src/components/decoder_block.rs:13-32 over
+crates/infer-core/src/component.rs:8-27).  h is fp32; pending is in the activation dtype.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, Optional
+
+import torch
+
+from .base import FEED_FORWARDS, MIXERS, NORMS, BuildContext, FeedForward, Mixer, Norm, StepContext
+from .spec import LayerSpec
+
+
+@dataclass
+class Hidden:
+    stream: torch.Tensor                # [T, hidden] fp32
+    pending: Optional[torch.Tensor]     # [T, hidden] activation dtype, not yet added
+
+
+class Block:
+    def __init__(self, spec: LayerSpec):
+        self.spec = spec
+        self.mixer: Mixer = MIXERS.build(spec.mixer)
+        self.mixer_norm: Norm = NORMS.build(spec.mixer_norm)
+        self.ffn: FeedForward = FEED_FORWARDS.build(spec.ffn)
+        self.ffn_norm: Norm = NORMS.build(spec.ffn_norm)
+        fn = ARRANGEMENTS.get(spec.arrangement)
+        if fn is None:
+            raise KeyError(f"no block arrangement '{spec.arrangement}'; known: {sorted(ARRANGEMENTS)}")
+        self._run = fn
+
+    def roles(self):
+        return {"mixer": self.mixer, "mixer_norm": self.mixer_norm, "ffn": self.ffn,
+                "ffn_norm": self.ffn_norm}
+
+    def prepare(self, ctx: BuildContext) -> None:
+        for part in self.roles().values():
+            part.prepare(ctx)
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.mixer.graph_safe and self.ffn.graph_safe
+
+    def forward(self, hidden: Hidden, step: StepContext, cache) -> None:
+        self._run(self, hidden, step, cache)
+
+
+def _pre_norm(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
+    x = block.mixer_norm.add_norm(hidden.stream, hidden.pending)
+    hidden.pending = block.mixer.forward(x, step, cache)
+    x = block.ffn_norm.add_norm(hidden.stream, hidden.pending)
+    hidden.pending = block.ffn.forward(x, step)
+
+
+ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm}
+
+
+def register_arrangement(name: str, fn: Callable) -> None:
+    ARRANGEMENTS[name] = fn

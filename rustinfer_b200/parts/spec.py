@@ -1,0 +1,80 @@
+"""The data that describes a model: which part stands where, with which numbers.
+
+A model is a tuple of `LayerSpec` plus a run order.  Each layer names its mixer,
+feed-forward and norms by the *kind* under which the part is registered and hands
+them their sizes and constants as `params`; nothing in a part refers to the model
+it sits in.  Layers may differ from one another, and the run order is data too: it
+may name a layer twice, or let a layer read the cache another layer wrote.
+
+RustInfer wires its decoder in code (crates/infer-worker/src/models/decoder.rs:214-410
+builds `Embed`, N x `DecoderBlock{Attention, DenseFfn}`, the final `RmsNorm` and
+`LmHead`); here the same wiring is a value that a configuration produces.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Mapping, Optional, Tuple
+
+
+def _freeze(value: Any) -> Any:
+    if isinstance(value, Mapping):
+        return tuple(sorted((k, _freeze(v)) for k, v in value.items()))
+    if isinstance(value, (list, tuple)):
+        return tuple(_freeze(v) for v in value)
+    return value
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """A part chosen by registered `kind`, with its parameters."""
+    kind: str
+    params: Mapping[str, Any] = field(default_factory=dict)
+
+    def key(self) -> Tuple:
+        """Hashable identity: two specs with the same key may share tables."""
+        return (self.kind, _freeze(self.params))
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One block: how mixer, feed-forward and norms are arranged, and the tensor-name
+    prefix of each (`names[role] + local_name` is the tensor's name in the file)."""
+    mixer: PartSpec
+    mixer_norm: PartSpec
+    ffn: PartSpec
+    ffn_norm: PartSpec
+    names: Mapping[str, str]            # roles: mixer, mixer_norm, ffn, ffn_norm
+    arrangement: str = "pre_norm"
+
+
+@dataclass(frozen=True)
+class RunEntry:
+    """One stop of the run order: run `layer`; `cache_of` names the layer whose cache
+    it reads and writes (None: its own).  A layer that reads another layer's cache
+    does not write keys of its own."""
+    layer: int
+    cache_of: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    hidden_size: int
+    vocab_size: int
+    layers: Tuple[LayerSpec, ...]
+    run_order: Tuple[RunEntry, ...]
+    final_norm: PartSpec
+    embed_name: str                     # prefix of the embedding table
+    final_norm_name: str
+    head_name: str
+    tie_head: bool                      # config says the head is the embedding table
+    eos_token_ids: Tuple[int, ...] = ()
+
+    def validate(self) -> None:
+        n = len(self.layers)
+        if n == 0:
+            raise ValueError("a model needs at least one layer")
+        for e in self.run_order:
+            if not 0 <= e.layer < n:
+                raise ValueError(f"run order names layer {e.layer}, model has {n}")
+            if e.cache_of is not None and not 0 <= e.cache_of < n:
+                raise ValueError(f"run order reads cache of layer {e.cache_of}, model has {n}")
