@@ -83,7 +83,8 @@ class ModelRunner:
 
     def __init__(self, model_dir: str, dtype="bfloat16", device="cuda:0", max_model_len: int = 4096,
                  page_size: int = 16, num_pages: Optional[int] = None, max_batch_seqs: int = 64,
-                 max_batch_tokens: int = 8192):
+                 max_batch_tokens: int = 8192, mem_fraction_static: float = 0.9,
+                 capture_sizes: Optional[Sequence[int]] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("rustinfer_b200 runs on a CUDA device (sm_100a) only; there is no CPU path")
         self.device = torch.device(device)
@@ -104,10 +105,11 @@ class ModelRunner:
 
         self.layout = CacheLayout.from_needs(self.model.cache_needs())
         self.max_pages_per_request = (self.max_model_len + self.page_size - 1) // self.page_size
-        if num_pages is None:
-            num_pages = self.max_batch_seqs * self.max_pages_per_request
-        self.num_pages = int(num_pages)
         paged = self.layout.paged_groups()
+        if num_pages is None:
+            num_pages = self._auto_pages(mem_fraction_static)
+        self.num_pages = int(num_pages)
+        self.capture_sizes = sorted(set(int(c) for c in (capture_sizes or ())))
         self.cache = CacheManager(self.layout, [self.num_pages] * len(paged), self.page_size,
                                   self.max_batch_seqs)
         self._alloc_storage()
@@ -121,6 +123,26 @@ class ModelRunner:
         self.steps_run = 0
 
     # ------------------------------------------------------------------------ storage
+    def _auto_pages(self, fraction: float) -> int:
+        """Pages per group from the memory that is free once the weights are loaded:
+        (free - 1 GiB) * fraction / bytes per page over all groups, at most what
+        max_batch_seqs requests of max_model_len tokens can use
+        (crates/infer-worker/src/application/serve_loop.rs:425-449)."""
+        esize = torch.empty((), dtype=self.dtype).element_size()
+        per_page = 0
+        for g in self.layout.groups:
+            if isinstance(g.need, PagedKV):
+                per_page += len(g.entries) * 2 * g.need.num_kv_heads * self.page_size * g.need.head_dim * esize
+        cap = self.max_batch_seqs * self.max_pages_per_request
+        if per_page == 0:
+            return 1
+        free, _total = torch.cuda.mem_get_info(self.device)
+        by_memory = int(max(0, free - (1 << 30)) * fraction) // per_page
+        if by_memory < self.max_pages_per_request:
+            raise RuntimeError(f"free GPU memory holds {by_memory} cache pages; one request of "
+                               f"max_model_len {self.max_model_len} needs {self.max_pages_per_request}")
+        return min(cap, by_memory)
+
     def _alloc_storage(self) -> None:
         self.group_storage: List[torch.Tensor] = []
         self._paged_index: Dict[int, int] = {}

@@ -1,0 +1,75 @@
+"""Choosing next tokens from logits on the device.
+
+All rows greedy: one argmax kernel, only the ids cross to the host
+(crates/infer-worker/src/application/runtime/mod.rs:713-758).  Otherwise one kernel sorts
+and filters each row in the order of RustInfer's host sampler
+(crates/infer-worker/src/application/sampler_stack.rs:242-351).  The uniform draw of a
+row is a function of (the request's seed, the position of the token being chosen) alone,
+so a request's tokens do not depend on which rows share its batch; the reference mixes
+the row index into the seed (:77-85), which makes them depend on it.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..ops import kernels as K
+from .params import SamplingParams
+
+_MASK = (1 << 64) - 1
+
+
+def _splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _MASK
+    z = x
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+def uniform_draw(seed: int, position: int) -> float:
+    """A double in [0, 1) from (seed, position): 53 bits of splitmix64."""
+    mixed = (seed ^ ((position * 0x9E3779B97F4A7C15) & _MASK)) & _MASK
+    return (_splitmix64(mixed) >> 11) * (1.0 / (1 << 53))
+
+
+def fresh_seed() -> int:
+    return int.from_bytes(os.urandom(8), "little")
+
+
+class Sampler:
+    def __init__(self, device: torch.device, vocab_size: int, max_rows: int):
+        self.device = device
+        self.vocab = vocab_size
+        self.max_rows = max_rows
+        self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
+        self._scratch: Optional[torch.Tensor] = None
+
+    def argmax_device(self, logits: torch.Tensor) -> torch.Tensor:
+        out = self._out[: logits.shape[0]]
+        K.argmax(logits, out)
+        return out
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+               positions: Sequence[int]) -> List[int]:
+        """logits fp32 [R, vocab]; row i is drawn with params[i], seeds[i] at positions[i]."""
+        R = logits.shape[0]
+        if R > self.max_rows:
+            raise ValueError(f"{R} rows exceed the sampler's {self.max_rows}")
+        if all(p.is_greedy() for p in params):
+            return self.argmax_device(logits).tolist()
+        if self._scratch is None:
+            self._scratch = torch.empty(K.sample_scratch_elems(self.max_rows, self.vocab),
+                                        dtype=torch.int64, device=self.device)
+        host_f = torch.tensor([[p.temperature if not p.is_greedy() else 0.0, p.top_p, p.min_p]
+                               for p in params], dtype=torch.float32)
+        host_k = torch.tensor([max(p.top_k, 0) for p in params], dtype=torch.int32)
+        host_u = torch.tensor([uniform_draw(s, pos) for s, pos in zip(seeds, positions)],
+                              dtype=torch.float64)
+        f = host_f.to(self.device, non_blocking=True)
+        out = self._out[:R]
+        K.sample(logits, self._scratch, f[:, 0].contiguous(), host_k.to(self.device), f[:, 1].contiguous(),
+                 f[:, 2].contiguous(), host_u.to(self.device), out)
+        return out.tolist()
