@@ -1,0 +1,341 @@
+"""Each CUDA kernel alone against a plain fp32/fp64 torch statement of the same op, at
+sizes other than the engine's tiny models: widths and vocabularies that are no power of
+two, several head sizes, page sizes and group counts."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def K():
+    from rustinfer_b200.ops import kernels
+    return kernels
+
+
+def tol(dtype):
+    # one rounding to the storage type on the way out, measured against a float64 statement
+    return 2e-6 if dtype == torch.float32 else 2 ** -8
+
+
+def close(got, ref, dtype, scale=None):
+    ref = ref.double().cpu()
+    scale = float(ref.abs().max()) if scale is None else scale
+    err = float((got.double().cpu() - ref).abs().max())
+    assert err <= tol(dtype) * max(scale, 1e-30), f"max err {err:.3e} vs scale {scale:.3e}"
+
+
+@pytest.mark.parametrize("tdt", DT)
+@pytest.mark.parametrize("d,vocab", [(72, 131), (1000, 517), (4100, 33)])
+def test_embed_gather(tdt, d, vocab):
+    torch.manual_seed(0)
+    table = torch.randn(vocab, d).to(tdt).to(dev())
+    ids = torch.randint(0, vocab, (37,), dtype=torch.int32, device=dev())
+    out = torch.empty(37, d, dtype=torch.float32, device=dev())
+    K().embed_gather(ids, table, out)
+    assert torch.equal(out.cpu(), P.embedding(table.cpu().double(), ids.tolist()).float())
+
+
+@pytest.mark.parametrize("adt", DT)
+@pytest.mark.parametrize("wdt", DT)
+@pytest.mark.parametrize("d", [80, 1000, 4100])
+def test_add_rmsnorm(adt, wdt, d):
+    torch.manual_seed(1)
+    T, eps = 19, 3e-6
+    h0 = (torch.randn(T, d) * 3).to(dev())
+    delta = torch.randn(T, d).to(adt).to(dev())
+    w = (1 + 0.3 * torch.randn(d)).to(wdt).to(dev())
+    # with delta: h is updated, out is the norm of the sum
+    h = h0.clone()
+    out = torch.empty(T, d, dtype=adt, device=dev())
+    K().add_rmsnorm(h, delta, w, eps, out)
+    s = h0.double().cpu() + delta.double().cpu()
+    assert torch.equal(h.cpu(), (h0 + delta.float()).cpu())           # the residual sum is fp32
+    close(out, P.rmsnorm(s, w.double().cpu(), eps), adt)
+    # without delta
+    h = h0.clone()
+    K().add_rmsnorm(h, None, w, eps, out)
+    assert torch.equal(h, h0)
+    close(out, P.rmsnorm(h0.double().cpu(), w.double().cpu(), eps), adt)
+    # rows: only the chosen rows, h untouched
+    rows = torch.tensor([18, 0, 7], dtype=torch.int32, device=dev())
+    h = h0.clone()
+    out3 = torch.empty(3, d, dtype=adt, device=dev())
+    K().add_rmsnorm(h, delta, w, eps, out3, rows)
+    assert torch.equal(h, h0)
+    close(out3, P.rmsnorm(s[rows.cpu().long()], w.double().cpu(), eps), adt)
+    K().residual_add(h, delta)
+    assert torch.equal(h.cpu(), (h0 + delta.float()).cpu())
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("inter", [24, 1001, 8192])
+def test_silu_mul(dt, inter):
+    torch.manual_seed(2)
+    gu = (torch.randn(11, 2 * inter) * 4).to(dt).to(dev())
+    out = torch.empty(11, inter, dtype=dt, device=dev())
+    K().silu_mul(gu, out)
+    g, u = gu.double().cpu()[:, :inter], gu.double().cpu()[:, inter:]
+    close(out, P.swiglu(g, u), dt)
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 130, 96), (37, 53, 129), (64, 64, 16), (70, 391, 272), (5, 1000, 1000)])
+def test_gemm_f32_is_exact_fp32(M, N, K_):
+    torch.manual_seed(3)
+    a = torch.randn(M, K_, device=dev())
+    w = torch.randn(N, K_, device=dev())
+    out = torch.empty(M, N, device=dev())
+    K().gemm_f32(a, w, out)
+    ref = a.double().cpu() @ w.double().cpu().T
+    # fp32 products summed in fp32: error grows like sqrt(K) * 2^-24 of the row norms; TF32
+    # inputs (10-bit mantissa) would miss this bound by three orders of magnitude
+    bound = 4 * math.sqrt(K_) * 2 ** -24 * float(a.norm(dim=1).max() * w.norm(dim=1).max())
+    assert float((out.double().cpu() - ref).abs().max()) <= bound
+    # a row's result does not depend on the other rows of the batch: bit for bit
+    one = torch.empty(1, N, device=dev())
+    K().gemm_f32(a[M // 2: M // 2 + 1], w, one)
+    assert torch.equal(one[0], out[M // 2])
+    # strided views (a column block of a wider buffer)
+    wide = torch.randn(M, K_ + 24, device=dev())
+    K().gemm_f32(wide[:, 8: 8 + K_], w, out)
+    assert torch.allclose(out.double().cpu(), wide[:, 8: 8 + K_].double().cpu() @ w.double().cpu().T, atol=bound)
+
+
+def _rope_tables(positions, rot, theta=10000.0):
+    f = P.rope_inv_freq(rot, theta, None)
+    ang = torch.arange(positions, dtype=torch.float64)[:, None] * f[None, :]
+    return torch.cos(ang), torch.sin(ang)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("Hq,Hkv,hd,rot,page", [(4, 2, 16, 16, 16), (3, 1, 32, 32, 8), (6, 3, 48, 48, 16),
+                                                (5, 5, 64, 32, 4), (8, 2, 128, 128, 32)])
+def test_rope_scatter(dt, Hq, Hkv, hd, rot, page):
+    torch.manual_seed(4)
+    T, pages, maxpos = 23, 9, 200
+    qkv0 = torch.randn(T, (Hq + 2 * Hkv) * hd).to(dt)
+    pos = torch.randint(0, maxpos, (T,), dtype=torch.int32)
+    c, s = _rope_tables(maxpos, rot)
+    slots = torch.randperm(pages * page)[:T].to(torch.int32)
+    slots[5] = -1                                                     # a token that is not stored
+    cache = torch.full((pages, 2, Hkv, page, hd), 7.0, dtype=dt, device=dev())
+    qkv = qkv0.clone().to(dev())
+    K().rope_scatter(qkv, pos.to(dev()), c.float().to(dev()), s.float().to(dev()), slots.to(dev()), cache,
+                     Hq, Hkv, hd, rot)
+    x = qkv0.double().view(T, Hq + 2 * Hkv, hd)
+    f = P.rope_inv_freq(rot, 10000.0, None)
+    rotated = torch.cat([P.rope_rotate(x[..., :rot], pos, f), x[..., rot:]], dim=-1)
+    got = qkv.double().cpu().view(T, Hq + 2 * Hkv, hd)
+    close(got[:, :Hq], rotated[:, :Hq], dt)
+    assert torch.equal(got[:, Hq:], x[:, Hq:])                        # k and v columns are left alone
+    want = torch.full((pages, 2, Hkv, page, hd), 7.0, dtype=torch.float64)
+    for t in range(T):
+        if slots[t] < 0:
+            continue
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        want[pg, 0, :, off] = rotated[t, Hq: Hq + Hkv]
+        want[pg, 1, :, off] = x[t, Hq + Hkv:]
+    close(cache, want, dt, scale=float(x.abs().max()))
+    untouched = want == 7.0
+    assert torch.equal(cache.double().cpu()[untouched], want[untouched])
+
+
+class PagedCase:
+    """A ragged batch laid out in a paged cache by hand, for the attention kernels."""
+
+    def __init__(self, dt, Hq, Hkv, hd, page, kv_lens, q_lens, seed=0, poison=True):
+        g = torch.Generator().manual_seed(seed)
+        self.dt, self.Hq, self.Hkv, self.hd, self.page = dt, Hq, Hkv, hd, page
+        self.kv_lens, self.q_lens = kv_lens, q_lens
+        B = len(kv_lens)
+        blocks = [(n + page - 1) // page for n in kv_lens]
+        n_pages = sum(blocks) + 3
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.k = [torch.randn(n, Hkv, hd, generator=g).to(dt) for n in kv_lens]
+        self.v = [torch.randn(n, Hkv, hd, generator=g).to(dt) for n in kv_lens]
+        self.q = [torch.randn(n, Hq, hd, generator=g).to(dt) for n in q_lens]
+        fill = float("nan") if poison else 0.0
+        cache = torch.full((n_pages, 2, Hkv, page, hd), fill, dtype=dt)
+        table = torch.zeros(B, max(blocks), dtype=torch.int32)
+        at = 0
+        for b in range(B):
+            for j in range(blocks[b]):
+                pg = perm[at]; at += 1
+                table[b, j] = pg
+                lo, hi = j * page, min((j + 1) * page, kv_lens[b])
+                cache[pg, 0, :, : hi - lo] = self.k[b][lo:hi].transpose(0, 1)
+                cache[pg, 1, :, : hi - lo] = self.v[b][lo:hi].transpose(0, 1)
+        self.cache, self.table = cache.to(dev()), table.to(dev())
+        cu = [0]
+        for n in q_lens:
+            cu.append(cu[-1] + n)
+        self.cu_q = torch.tensor(cu, dtype=torch.int32, device=dev())
+        self.kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=dev())
+        self.q_all = torch.cat(self.q).reshape(cu[-1], Hq * hd).to(dev())
+
+    def tiles(self, rows):
+        te, tq = [], []
+        for b, n in enumerate(self.q_lens):
+            for j in range(0, n, rows):
+                te.append(b); tq.append(j)
+        return (torch.tensor(te, dtype=torch.int32, device=dev()),
+                torch.tensor(tq, dtype=torch.int32, device=dev()))
+
+    def reference(self, scale, window=None):
+        outs = []
+        for b, (n_kv, n_q) in enumerate(zip(self.kv_lens, self.q_lens)):
+            # the entry's queries are the last n_q positions of its n_kv keys
+            qfull = torch.zeros(n_kv, self.Hq, self.hd, dtype=torch.float64)
+            qfull[n_kv - n_q:] = self.q[b].double()
+            o = P.causal_gqa_attention(qfull, self.k[b].double(), self.v[b].double(), scale, window)
+            outs.append(o[n_kv - n_q:])
+        return torch.cat(outs).reshape(-1, self.Hq * self.hd)
+
+
+ATT_SHAPES = [(4, 2, 16, 16), (3, 1, 32, 8), (6, 3, 48, 16), (8, 2, 64, 16), (4, 4, 128, 32),
+              (2, 1, 256, 16), (10, 5, 80, 4)]
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("Hq,Hkv,hd,page", ATT_SHAPES)
+def test_attention_plain_ragged(dt, Hq, Hkv, hd, page):
+    # whole prompts, portions that start mid-page, single decode tokens, lengths at page edges
+    kv_lens = [1, 17, 64, 65, 130, 33, 16]
+    q_lens = [1, 17, 1, 2, 41, 33, 1]
+    case = PagedCase(dt, Hq, Hkv, hd, page, kv_lens, q_lens, seed=hd)
+    out = torch.empty_like(case.q_all)
+    te, tq = case.tiles(16)
+    scale = 1 / math.sqrt(hd)
+    K().attention_plain(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                        Hq, Hkv, hd, scale, None)
+    close(out, case.reference(scale), dt)
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("window", [1, 5, 16, 40])
+def test_attention_plain_window(dt, window):
+    case = PagedCase(dt, 4, 2, 32, 8, [70, 9, 40], [30, 9, 1], seed=window)
+    out = torch.empty_like(case.q_all)
+    te, tq = case.tiles(16)
+    K().attention_plain(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                        4, 2, 32, 0.2, window)
+    close(out, case.reference(0.2, window), dt)
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_attention_plain_finds_one_far_key(dt):
+    """One key among hundreds carries the whole score: the output must be its value.
+    A kernel that skips a page, a chunk or a page's last slot gets this visibly wrong."""
+    Hq, Hkv, hd, page = 2, 1, 64, 16
+    for far in (0, 15, 16, 63, 64, 255, 300, 310):
+        case = PagedCase(dt, Hq, Hkv, hd, page, [311], [1], seed=far, poison=True)
+        k = case.k[0].double()
+        qv = (k[far, 0] / k[far, 0].norm() * 60.0)
+        case.q_all = qv.repeat(Hq).to(dt).reshape(1, Hq * hd).to(dev())
+        out = torch.empty_like(case.q_all)
+        te, tq = case.tiles(16)
+        K().attention_plain(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                            Hq, Hkv, hd, 1.0, None)
+        want = case.v[0][far, 0].double().repeat(Hq)
+        assert float((out.double().cpu()[0] - want).abs().max()) < 0.05, far
+
+
+def test_attention_plain_is_bitwise_cut_invariant():
+    """fp32: the same positions computed as one portion, as two, or token by token give the
+    same bits, because keys are always visited in the same chunks from key 0."""
+    Hq, Hkv, hd, page = 4, 2, 32, 8
+    whole = PagedCase(torch.float32, Hq, Hkv, hd, page, [150], [150], seed=1, poison=False)
+    out = torch.empty_like(whole.q_all)
+    te, tq = whole.tiles(16)
+    K().attention_plain(whole.q_all, out, whole.cache, whole.table, whole.cu_q, whole.kv_len, te, tq,
+                        Hq, Hkv, hd, 0.3, None)
+    for start, n in [(0, 7), (7, 50), (57, 1), (58, 92), (149, 1)]:
+        cu = torch.tensor([0, n], dtype=torch.int32, device=dev())
+        kvl = torch.tensor([start + n], dtype=torch.int32, device=dev())
+        q = whole.q_all[start: start + n].contiguous()
+        o = torch.empty_like(q)
+        tiles_e = torch.zeros((n + 15) // 16, dtype=torch.int32, device=dev())
+        tiles_q = torch.arange(0, n, 16, dtype=torch.int32, device=dev())
+        K().attention_plain(q, o, whole.cache, whole.table, cu, kvl, tiles_e, tiles_q, Hq, Hkv, hd, 0.3, None)
+        assert torch.equal(o, out[start: start + n])
+
+
+@pytest.mark.parametrize("V", [130, 391, 128256])
+def test_argmax_lowest_index_wins(V):
+    torch.manual_seed(5)
+    logits = torch.randn(5, V, device=dev())
+    logits[1, 7] = logits[1, V - 1] = 50.0
+    logits[2, :] = 0.0
+    logits[3, V - 1] = 60.0
+    logits[4, 3] = float("nan")
+    out = torch.empty(5, dtype=torch.int32, device=dev())
+    K().argmax(logits, out)
+    want = [P.argmax_lowest(torch.nan_to_num(r, nan=-1e30)) for r in logits.cpu()]
+    assert out.tolist() == want and out[1] == 7 and out[2] == 0 and out[3] == V - 1
+
+
+@pytest.mark.parametrize("V", [130, 391, 5000])
+def test_sample_matches_the_plain_sampler(V):
+    g = torch.Generator().manual_seed(V)
+    combos = [(0.8, 0, 1.0, 0.0), (1.0, 5, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
+              (0.9, 40, 0.8, 0.01), (0.0, 0, 1.0, 0.0), (1.0, 1, 1.0, 0.0), (1.0, 0, 0.0, 0.0),
+              (2.0, 3, 0.5, 0.2)]
+    rows = []
+    for rep in range(4):
+        for c in combos:
+            rows.append(c)
+    R = len(rows)
+    logits = (torch.randn(R, V, generator=g) * 3)
+    logits[3, 10] = logits[3, 20] = logits[3].max() + 1          # equal logits: ascending id
+    draws = torch.rand(R, generator=g, dtype=torch.float64)
+    k = K()
+    scratch = torch.empty(k.sample_scratch_elems(R, V), dtype=torch.int64, device=dev())
+    out = torch.empty(R, dtype=torch.int32, device=dev())
+    f = lambda i, dt: torch.tensor([r[i] for r in rows], dtype=dt, device=dev())
+    k.sample(logits.to(dev()), scratch, f(0, torch.float32), f(1, torch.int32), f(2, torch.float32),
+             f(3, torch.float32), draws.to(dev()), out)
+    want = [P.sample_filtered(logits[i], *rows[i], float(draws[i])) for i in range(R)]
+    assert out.tolist() == want
+
+
+def test_sample_distribution_and_filters():
+    """Many draws over a small row: frequencies follow softmax(logits/T) within the kept set."""
+    V, R = 8, 4000
+    base = torch.tensor([2.0, 1.0, 0.5, 0.0, -0.5, -1.0, -3.0, -8.0])
+    logits = base.repeat(R, 1).to(dev())
+    k = K()
+    scratch = torch.empty(k.sample_scratch_elems(R, V), dtype=torch.int64, device=dev())
+    out = torch.empty(R, dtype=torch.int32, device=dev())
+    from rustinfer_b200.sampling.sampler import uniform_draw
+    draws = torch.tensor([uniform_draw(11, p) for p in range(R)], dtype=torch.float64, device=dev())
+    full = lambda v, dt: torch.full((R,), v, dtype=dt, device=dev())
+    k.sample(logits, scratch, full(0.7, torch.float32), full(4, torch.int32), full(1.0, torch.float32),
+             full(0.0, torch.float32), draws, out)
+    counts = torch.bincount(out.cpu().long(), minlength=V).double()
+    assert counts[4:].sum() == 0                                    # top-k 4
+    p = torch.softmax(base[:4].double() / 0.7, dim=0)
+    assert torch.allclose(counts[:4] / R, p, atol=0.03)
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from rustinfer_b200.ops.library import KernelError
+    k = K()
+    with pytest.raises(KernelError, match="CUDA tensors"):
+        k.silu_mul(torch.zeros(2, 4), torch.zeros(2, 2))
+    with pytest.raises(KernelError, match="multiples of 16"):
+        from rustinfer_b200.ops import library
+        library.attention_plain(24)
+    with pytest.raises(KernelError):
+        k.gemm_f32(torch.zeros(2, 3, device=dev()), torch.zeros(4, 5, device=dev()), torch.zeros(2, 4, device=dev()))
+    with pytest.raises(KernelError):
+        k.add_rmsnorm(torch.zeros(2, 8, device=dev()), None, torch.ones(9, device=dev()), 1e-5,
+                      torch.zeros(2, 8, device=dev()))

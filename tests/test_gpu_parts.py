@@ -1,0 +1,266 @@
+"""Each part of the decoder alone against the plain implementation, and a toy mixer with
+state of its own that is registered, built and stepped from this file alone."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+import plain_llama as P
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+DT = [torch.float32, torch.bfloat16]
+TOLP = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def ctx(dtype, max_len=256, page=8):
+    from rustinfer_b200.parts.base import BuildContext
+    return BuildContext(dev(), dtype, max_len, page)
+
+
+def one_sequence_step(T, page, n_groups=1):
+    """A StepContext for one whole sequence of T tokens laid out in pages 3, 4, 5, ..."""
+    from rustinfer_b200.parts.base import GroupStep, HostEntry, StepContext
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    blocks = (T + page - 1) // page
+    table = i32([[3 + b for b in range(blocks)]])
+    slot = i32([(3 + t // page) * page + t % page for t in range(T)])
+    tiles = {16: (i32([0] * ((T + 15) // 16)), i32(list(range(0, T, 16))))}
+    return StepContext(num_tokens=T, num_entries=1, token_ids=i32([0] * T), positions=i32(list(range(T))),
+                       cu_q=i32([0, T]), kv_len=i32([T]), state_slots=i32([0]),
+                       groups=[GroupStep(table, slot) for _ in range(n_groups)], tiles=tiles,
+                       entries=[HostEntry("x", 0, T, 0)], max_q_len=T, max_kv_len=T, decode_only=False)
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_rmsnorm_part(dt):
+    from rustinfer_b200.parts.base import NORMS
+    from rustinfer_b200.parts.spec import PartSpec
+    torch.manual_seed(0)
+    part = NORMS.build(PartSpec("rmsnorm", {"size": 104, "eps": 2e-6}))
+    assert {n: d.shape for n, d in part.param_decls().items()} == {"weight": (104,)}
+    part.prepare(ctx(dt))
+    w = (1 + 0.2 * torch.randn(104)).to(dt)
+    part.load({"weight": w.to(dev())})
+    h = torch.randn(9, 104, device=dev())
+    delta = torch.randn(9, 104).to(dt).to(dev())
+    want_h = h.double().cpu() + delta.double().cpu()
+    out = part.add_norm(h, delta)
+    assert out.dtype == dt
+    assert rel_err(out, P.rmsnorm(want_h, w.double(), 2e-6)) <= TOLP[dt]
+    assert rel_err(h, want_h) <= 1e-6
+
+
+@pytest.mark.parametrize("dt", DT)
+def test_swiglu_part(dt):
+    from rustinfer_b200.parts.base import FEED_FORWARDS
+    from rustinfer_b200.parts.spec import PartSpec
+    torch.manual_seed(1)
+    d, inter = 80, 104
+    part = FEED_FORWARDS.build(PartSpec("swiglu", {"hidden_size": d, "intermediate_size": inter}))
+    assert {n: v.shape for n, v in part.param_decls().items()} == {
+        "gate_proj.weight": (inter, d), "up_proj.weight": (inter, d), "down_proj.weight": (d, inter)}
+    part.prepare(ctx(dt))
+    w = {n: (torch.randn(v.shape) / math.sqrt(v.shape[1])).to(dt) for n, v in part.param_decls().items()}
+    part.load({n: t.to(dev()) for n, t in w.items()})
+    x = torch.randn(13, d).to(dt)
+    y = part.forward(x.to(dev()), None)
+    xd = x.double()
+    m = P.swiglu(xd @ w["gate_proj.weight"].double().T, xd @ w["up_proj.weight"].double().T)
+    assert rel_err(y, m @ w["down_proj.weight"].double().T) <= TOLP[dt]
+
+
+def test_linear_keeps_32_bit_weights_in_a_bfloat16_engine():
+    from rustinfer_b200.parts.linear import Linear
+    torch.manual_seed(2)
+    w = torch.randn(37, 96)
+    x = torch.randn(5, 96).bfloat16()
+    ref = x.double() @ w.double().T
+    y32 = Linear(w.to(dev()))(x.to(dev()), out_dtype=torch.float32)
+    # exact in the weight: only x was rounded (it is the same x), so the error is fp32-sized
+    assert rel_err(y32, ref) <= 1e-6
+    ybf = Linear(w.bfloat16().to(dev()))(x.to(dev()), out_dtype=torch.float32)
+    assert 1e-4 < rel_err(ybf, ref) <= 2e-2               # rounding the weight shows
+    assert Linear(w.to(dev()))(x.to(dev())).dtype == torch.bfloat16
+
+
+def test_rotary_part_tables_on_the_device():
+    from rustinfer_b200.parts.base import POSITIONS
+    from rustinfer_b200.parts.spec import PartSpec
+    scaling = dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                   original_max_position_embeddings=64)
+    part = POSITIONS.build(PartSpec("rope", {"head_dim": 32, "rotary_dim": 32, "theta": 5e5, "scaling": scaling}))
+    part.prepare(ctx(torch.bfloat16, max_len=300))
+    assert part.cos.dtype == torch.float32 and part.cos.shape == (300, 16)      # fp32 whatever the engine
+    f = P.rope_inv_freq(32, 5e5, scaling)
+    ang = torch.arange(300, dtype=torch.float64)[:, None] * f[None, :]
+    assert float((part.cos.double().cpu() - torch.cos(ang)).abs().max()) <= 2 ** -24
+    assert float((part.sin.double().cpu() - torch.sin(ang)).abs().max()) <= 2 ** -24
+
+
+@pytest.mark.parametrize("dt", DT)
+@pytest.mark.parametrize("Hq,Hkv,hd,window", [(6, 3, 48, None), (4, 1, 32, None), (4, 2, 16, 11)])
+def test_attention_part(dt, Hq, Hkv, hd, window):
+    from rustinfer_b200.parts.base import MIXERS, PagedKV, PagedLayerCache
+    from rustinfer_b200.parts.spec import PartSpec
+    torch.manual_seed(3)
+    d, T, page = 72, 45, 8
+    rope = PartSpec("rope", {"head_dim": hd, "rotary_dim": hd, "theta": 10000.0, "scaling": None})
+    part = MIXERS.build(PartSpec("gqa_attention", {"hidden_size": d, "num_heads": Hq, "num_kv_heads": Hkv,
+                                                   "head_dim": hd, "scale": 0.21, "window": window,
+                                                   "position": rope}))
+    assert part.cache_need() == PagedKV(Hkv, hd, window)
+    part.prepare(ctx(dt, page=page))
+    w = {n: (torch.randn(v.shape) * (2.0 if n[0] in "qk" else 1.0) / math.sqrt(v.shape[1])).to(dt)
+         for n, v in part.param_decls().items()}
+    part.load({n: t.to(dev()) for n, t in w.items()})
+    x = torch.randn(T, d).to(dt)
+    cache = torch.full((12, 2, Hkv, page, hd), float("nan"), dtype=dt, device=dev())
+    y = part.forward(x.to(dev()), one_sequence_step(T, page), PagedLayerCache(cache, 0, True))
+    xd, wd = x.double(), {n: t.double() for n, t in w.items()}
+    f = P.rope_inv_freq(hd, 10000.0, None)
+    pos = torch.arange(T)
+    q = P.rope_rotate((xd @ wd["q_proj.weight"].T).view(T, Hq, hd), pos, f)
+    k = P.rope_rotate((xd @ wd["k_proj.weight"].T).view(T, Hkv, hd), pos, f)
+    v = (xd @ wd["v_proj.weight"].T).view(T, Hkv, hd)
+    a = P.causal_gqa_attention(q, k, v, 0.21, window).reshape(T, Hq * hd)
+    assert rel_err(y, a @ wd["o_proj.weight"].T) <= TOLP[dt]
+    # what it left in the cache: rotated keys and plain values at the slots of the table
+    got_k = cache[3: 3 + (T + page - 1) // page, 0].permute(0, 2, 1, 3).reshape(-1, Hkv, hd)[:T]
+    assert rel_err(got_k, k) <= TOLP[dt]
+
+
+# ------------------------------------------------------------------ a toy architecture
+# A mixer with fixed-size state of its own (an exponential moving sum of its inputs), put
+# into a model beside ordinary attention layers.  Everything it needs is in this file: the
+# mixer class, the configuration, the registry entry, and the plain statement of what it
+# computes.  No file of the framework knows it.
+
+def _register_toy():
+    from rustinfer_b200.config.registry import ArchitectureFamily, register_architecture
+    from rustinfer_b200.parts.base import FixedState, Mixer, ParamDecl, register_mixer
+    from rustinfer_b200.parts.linear import Linear
+    from rustinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+    @register_mixer("toy_moving_sum")
+    class MovingSum(Mixer):
+        """s_t = decay * s_{t-1} + x_t (fp32, per request); y_t = W s_t."""
+        graph_safe = False                    # it walks the entries on the host
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.d, self.decay = int(params["hidden_size"]), float(params["decay"])
+
+        def param_decls(self):
+            return {"mix.weight": ParamDecl((self.d, self.d))}
+
+        def cache_need(self):
+            return FixedState((self.d,), "float32")
+
+        def load(self, tensors):
+            self.mix = Linear(tensors["mix.weight"])
+
+        def forward(self, x, step, cache):
+            states = torch.empty((x.shape[0], self.d), dtype=torch.float32, device=x.device)
+            row = 0
+            for e in step.entries:
+                s = cache.state[e.slot]
+                for j in range(e.q_len):
+                    s = self.decay * s + x[row + j].float()
+                    states[row + j] = s
+                cache.state[e.slot] = s
+                row += e.q_len
+            return self.mix(states.to(x.dtype), out_dtype=x.dtype)
+
+    def spec_of(cfg):
+        d = cfg["hidden_size"]
+        norm = PartSpec("rmsnorm", {"size": d, "eps": cfg["eps"]})
+        ffn = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": cfg["intermediate_size"]})
+        rope = PartSpec("rope", {"head_dim": 16, "rotary_dim": 16, "theta": 10000.0, "scaling": None})
+        att = PartSpec("gqa_attention", {"hidden_size": d, "num_heads": d // 16, "num_kv_heads": 1, "head_dim": 16,
+                                         "scale": 0.25, "window": None, "position": rope})
+        toy = PartSpec("toy_moving_sum", {"hidden_size": d, "decay": cfg["decay"]})
+        layers = []
+        for i, kind in enumerate(cfg["mixers"]):
+            p = f"layers.{i}."
+            layers.append(LayerSpec(mixer=toy if kind == "toy" else att, mixer_norm=norm, ffn=ffn, ffn_norm=norm,
+                                    names={"mixer": p + "mixer.", "mixer_norm": p + "norm1.", "ffn": p + "mlp.",
+                                           "ffn_norm": p + "norm2."}))
+        return ModelSpec(hidden_size=d, vocab_size=cfg["vocab_size"], layers=tuple(layers),
+                         run_order=tuple(RunEntry(i) for i in range(len(layers))), final_norm=norm,
+                         embed_name="embed.", final_norm_name="norm.", head_name="head.", tie_head=True)
+
+    register_architecture(["ToyMovingSumLM"], ArchitectureFamily("toy", lambda c, g: dict(c), spec_of))
+
+
+def _toy_plain(cfg, w, ids):
+    """Whole sequence, float64, from the definitions above and the plain Llama parts."""
+    d = cfg["hidden_size"]
+    T = len(ids)
+    h = P.embedding(w["embed.weight"], ids)
+    f = P.rope_inv_freq(16, 10000.0, None)
+    pos = torch.arange(T)
+    for i, kind in enumerate(cfg["mixers"]):
+        p = f"layers.{i}."
+        x = P.rmsnorm(h, w[p + "norm1.weight"], cfg["eps"])
+        if kind == "toy":
+            s = torch.zeros(d, dtype=torch.float64)
+            rows = []
+            for t in range(T):
+                s = cfg["decay"] * s + x[t]
+                rows.append(s)
+            h = h + torch.stack(rows) @ w[p + "mixer.mix.weight"].T
+        else:
+            Hq = d // 16
+            q = P.rope_rotate((x @ w[p + "mixer.q_proj.weight"].T).view(T, Hq, 16), pos, f)
+            k = P.rope_rotate((x @ w[p + "mixer.k_proj.weight"].T).view(T, 1, 16), pos, f)
+            v = (x @ w[p + "mixer.v_proj.weight"].T).view(T, 1, 16)
+            a = P.causal_gqa_attention(q, k, v, 0.25).reshape(T, d)
+            h = h + a @ w[p + "mixer.o_proj.weight"].T
+        x = P.rmsnorm(h, w[p + "norm2.weight"], cfg["eps"])
+        m = P.swiglu(x @ w[p + "mlp.gate_proj.weight"].T, x @ w[p + "mlp.up_proj.weight"].T)
+        h = h + m @ w[p + "mlp.down_proj.weight"].T
+    return P.rmsnorm(h, w["norm.weight"], cfg["eps"]) @ w["embed.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
+    from rustinfer_b200.engine.runner import ModelRunner, StepEntry
+    from rustinfer_b200.weights.random_init import write_random_model
+    _register_toy()
+    cfg = {"architectures": ["ToyMovingSumLM"], "hidden_size": 48, "intermediate_size": 72, "vocab_size": 97,
+           "eps": 1e-5, "decay": 0.8, "mixers": ["toy", "attention", "toy"]}
+    folder = write_random_model(str(tmp_path / "toy"), cfg, seed=5, std=0.15, norm_std=0.2)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    r = ModelRunner(folder, dtype=dtype, max_model_len=128, page_size=8, num_pages=16, max_batch_seqs=3,
+                    max_batch_tokens=128)
+    from rustinfer_b200.parts.base import FixedState, PagedKV
+    assert [type(g.need) for g in r.layout.groups] == [FixedState, PagedKV]
+    assert r.layout.groups[0].entries == [0, 2] and not r.model.graph_safe
+    _, w = P.read_model_folder(folder)
+    g = torch.Generator().manual_seed(0)
+    a, b = (torch.randint(0, 97, (n,), generator=g).tolist() for n in (40, 23))
+    tol = 2e-5 if dtype == "float32" else 4e-2
+    # two requests, cut differently and mixed in the same steps; state must carry across cuts
+    r.open("a"), r.open("b")
+    got_a, got_b = [], []
+    plan = [([0, 10], [0, 1]), ([10, 11], [1, 20]), ([11, 30], [20, 21]), ([30, 40], [21, 23])]
+    for (a0, a1), (b0, b1) in plan:
+        lg = r.step([StepEntry("a", a[a0:a1], list(range(a1 - a0))), StepEntry("b", b[b0:b1], list(range(b1 - b0)))])
+        got_a.append(lg[: a1 - a0]); got_b.append(lg[a1 - a0:])
+    assert rel_err(torch.cat(got_a), _toy_plain(cfg, w, a)) <= tol
+    assert rel_err(torch.cat(got_b), _toy_plain(cfg, w, b)) <= tol
+    # a slot that is used again starts from zero state
+    r.close("a")
+    r.open("c")
+    assert r.cache.slot("c") == 0
+    lg = r.step([StepEntry("c", b, list(range(len(b))))])
+    assert rel_err(lg, _toy_plain(cfg, w, b)) <= tol
