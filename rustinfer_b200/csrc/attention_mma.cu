@@ -1,0 +1,520 @@
+// Paged causal GQA attention in bf16 on the tensor cores (mma.sync m16n8k16, fp32
+// accumulate), compiled for one RI_HEAD_DIM (a multiple of 16, at most 256).  Scores,
+// softmax and the output accumulators are fp32; probabilities are rounded to bf16 for
+// the P*V product, as in RustInfer's flash kernels
+// (crates/infer-backend-cuda/src/kernels/flash_attn_gqa/flash_attn_paged_prefill.cu:442-511).
+//
+// Two kernels share the tile loader and the fragment code:
+//
+//  prefill  one CTA = 64 rows x one kv head, a row being (query token, q head of the kv
+//           head's group), so the heads of a group share every K/V tile that is loaded
+//           (the reference runs one CTA per q head, :539-568, and fetches K/V with
+//           synchronous scalar loads, :379-407).  4 warps x 16 rows; K/V tiles of 64 keys
+//           gathered page by page with cp.async into a double buffer.
+//  decode   one CTA = the q heads of one kv head for one request's single new token and
+//           one split of its keys; the 4 warps take 16 keys each of every 64-key tile and
+//           merge their online-softmax states at the end.  With several splits the partial
+//           outputs and log-sum-exps go to scratch and a second kernel combines them
+//           (split-KV as in flash_attn_paged_decode.cu:75-340, but with the group's heads
+//           as the M dimension of the MMA instead of scalar dot products).
+//
+// Cache layout of one layer: [page][K|V][kv head][slot in page][head_dim], so a page's
+// keys of one head are one contiguous run.
+#include "common.cuh"
+
+#ifndef RI_HEAD_DIM
+#error "compile with -DRI_HEAD_DIM=<head size>"
+#endif
+
+namespace {
+constexpr int HD = RI_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "mma attention: head size multiple of 16, at most 256");
+constexpr int KT = 64;                 // keys per tile
+constexpr int ROW = HD + 8;            // padded smem row (elements): rows shift by 16 B, ldmatrix is conflict-free
+constexpr int CH = HD / 8;             // 16-byte chunks per row
+constexpr int KS = HD / 16;            // k-steps of Q*K^T
+constexpr int NT = HD / 8;             // n-tiles of the output
+constexpr int THREADS = 128;
+constexpr int MT = 64;                 // rows per prefill CTA
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int n = valid ? 16 : 0;      // 0 bytes read: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+
+// K and V rows of keys k0 .. k0+KT-1 of one kv head into smem; keys outside [k_lo, k_hi)
+// are zero-filled and their pages are never looked up.
+__device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ cache,
+                                             const int* __restrict__ bt, int k0, int k_lo, int k_hi,
+                                             int Hkv, int kvh, int page_size) {
+    const size_t head_step = (size_t)page_size * HD;
+    for (int c = threadIdx.x; c < KT * CH; c += THREADS) {
+        const int kk = c / CH, ch = c - kk * CH;
+        const int key = k0 + kk;
+        const bool ok = key >= k_lo && key < k_hi;
+        const bf16* sk = cache;
+        const bf16* sv = cache;
+        if (ok) {
+            const int page = bt[key / page_size], off = key % page_size;
+            sk = cache + ((size_t)(page * 2) * Hkv + kvh) * head_step + (size_t)off * HD + ch * 8;
+            sv = sk + (size_t)Hkv * head_step;
+        }
+        cp_async16(Ks + kk * ROW + ch * 8, sk, ok);
+        cp_async16(Vs + kk * ROW + ch * 8, sv, ok);
+    }
+}
+
+// ================================================================== prefill / ragged
+__global__ void __launch_bounds__(THREADS)
+prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+               const bf16* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
+               const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+               const int* __restrict__ tile_entry, const int* __restrict__ tile_tok0,
+               int Hq, int Hkv, int Gc, int chunks, int tpt, int page_size, float scale_log2, int window) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);            // [MT][ROW]
+    bf16* KVs = Qs + MT * ROW;                               // [2 buffers][K|V][KT][ROW]
+
+    const int b = tile_entry[blockIdx.x];
+    if (b < 0) return;
+    const int tok0 = tile_tok0[blockIdx.x];
+    const int G = Hq / Hkv;
+    const int kvh = blockIdx.y / chunks, hc = blockIdx.y - kvh * chunks;
+    const int head0 = kvh * G + hc * Gc;
+    const int nheads = min(Gc, G - hc * Gc);
+    const int q_begin = cu_q[b], q_len = cu_q[b + 1] - q_begin;
+    const int kvl = kv_len[b];
+    const int pos0 = kvl - q_len;
+    const int ntok = min(tpt, q_len - tok0);
+    if (ntok <= 0) return;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // Q rows: row r = (token tok0 + r / Gc, head head0 + r % Gc)
+    for (int c = tid; c < MT * CH; c += THREADS) {
+        const int r = c / CH, ch = c - r * CH;
+        const int jj = r / Gc, hh = r - jj * Gc;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (jj < ntok && hh < nheads)
+            v = *reinterpret_cast<const uint4*>(q + (size_t)(q_begin + tok0 + jj) * q_stride +
+                                                (size_t)(head0 + hh) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + r * ROW + ch * 8) = v;
+    }
+
+    const int p_first = pos0 + tok0, p_last = p_first + ntok - 1;
+    const int lo_tile = window > 0 ? max(0, p_first - window + 1) : 0;
+    const int t_begin = lo_tile / KT, t_end = p_last / KT + 1;
+    const int* bt = block_table + (size_t)b * table_stride;
+
+    load_kv_tile(KVs, KVs + KT * ROW, cache, bt, t_begin * KT, lo_tile, p_last + 1, Hkv, kvh, page_size);
+    cp_async_commit();
+    __syncthreads();                                          // Qs is written
+
+    // this thread's two rows: r0 = 16*warp + lane/4 and r0 + 8
+    int p_row[2], lo_row[2];
+    bool ok_row[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = warp * 16 + (lane >> 2) + 8 * i;
+        const int jj = r / Gc, hh = r - jj * Gc;
+        ok_row[i] = jj < ntok && hh < nheads;
+        p_row[i] = p_first + jj;
+        lo_row[i] = window > 0 ? max(0, p_row[i] - window + 1) : 0;
+    }
+
+    unsigned qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+        ldmatrix_x4(qf[ks], Qs + (warp * 16 + (lane & 15)) * ROW + ks * 16 + (lane >> 4) * 8);
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int buf = (t - t_begin) & 1;
+        bf16* Ks = KVs + buf * 2 * KT * ROW;
+        bf16* Vs = Ks + KT * ROW;
+        if (t + 1 < t_end) {
+            bf16* Kn = KVs + (buf ^ 1) * 2 * KT * ROW;
+            load_kv_tile(Kn, Kn + KT * ROW, cache, bt, (t + 1) * KT, lo_tile, p_last + 1, Hkv, kvh, page_size);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+
+        float s[KT / 8][4];
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < KT / 16; ++np) {
+                unsigned kf[4];
+                ldmatrix_x4(kf, Ks + (np * 16 + (lane & 7) + (lane >> 4) * 8) * ROW + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[2 * np], qf[ks], kf[0], kf[1]);
+                mma_bf16(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+            }
+        }
+        const int key0 = t * KT + (lane & 3) * 2;
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + n * 8 + (e & 1);
+                const int i = e >> 1;
+                const bool seen = ok_row[i] && key <= p_row[i] && key >= lo_row[i];
+                s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
+                mx[i] = fmaxf(mx[i], s[n][e]);
+            }
+        }
+        float alpha[2], muse[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            const float mnew = fmaxf(m[i], mx[i]);
+            muse[i] = mnew == -INFINITY ? 0.f : mnew;
+            alpha[i] = exp2f(m[i] - muse[i]);
+            m[i] = mnew;
+            l[i] *= alpha[i];
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+            o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+        }
+#pragma unroll
+        for (int n = 0; n < KT / 8; ++n) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[n][e] = exp2f(s[n][e] - muse[e >> 1]);
+                l[e >> 1] += s[n][e];
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+            unsigned pa[4];
+            pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            pa[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            pa[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                unsigned vf[4];
+                ldmatrix_x4_trans(vf, Vs + (kk * 16 + (lane & 15)) * ROW + np * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * np], pa, vf[0], vf[1]);
+                mma_bf16(o[2 * np + 1], pa, vf[2], vf[3]);
+            }
+        }
+        __syncthreads();                                      // all warps are done with this buffer
+    }
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        if (!ok_row[i]) continue;
+        const int r = warp * 16 + (lane >> 2) + 8 * i;
+        const int jj = r / Gc, hh = r - jj * Gc;
+        const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+        bf16* dst = out + (size_t)(q_begin + tok0 + jj) * out_stride + (size_t)(head0 + hh) * HD + (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+            *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    }
+}
+
+// ========================================================================== decode
+// grid (kv heads * head chunks, splits, decode entries).  part_o [entries][Hq][splits][HD]
+// fp32 and part_lse [entries][Hq][splits] (base-2 log-sum-exp) are written when splits > 1.
+__global__ void __launch_bounds__(THREADS)
+decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+              const bf16* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
+              const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+              const int* __restrict__ entry_list, int Hq, int Hkv, int Gc, int chunks, int page_size,
+              float scale_log2, int window, int splits, float* __restrict__ part_o,
+              float* __restrict__ part_lse) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);            // [16][ROW]
+    bf16* KVs = Qs + 16 * ROW;                               // [2][K|V][KT][ROW]
+
+    const int slot = blockIdx.z;
+    const int b = entry_list ? entry_list[slot] : slot;
+    if (b < 0) return;
+    const int split = blockIdx.y;
+    const int G = Hq / Hkv;
+    const int kvh = blockIdx.x / chunks, hc = blockIdx.x - kvh * chunks;
+    const int head0 = kvh * G + hc * Gc;
+    const int nheads = min(Gc, G - hc * Gc);
+    const int tok = cu_q[b + 1] - 1;                          // the entry's (last) token row
+    const int kvl = kv_len[b];
+    const int lo = window > 0 ? max(0, kvl - window) : 0;
+    const int t_first = lo / KT, t_count = (kvl + KT - 1) / KT - t_first;
+    const int per = (t_count + splits - 1) / splits;
+    const int t_begin = t_first + split * per, t_end = min(t_begin + per, t_first + t_count);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int* bt = block_table + (size_t)b * table_stride;
+
+    if (t_begin < t_end) {
+        load_kv_tile(KVs, KVs + KT * ROW, cache, bt, t_begin * KT, lo, kvl, Hkv, kvh, page_size);
+        cp_async_commit();
+    }
+    for (int c = tid; c < 16 * CH; c += THREADS) {
+        const int r = c / CH, ch = c - r * CH;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < nheads)
+            v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(head0 + r) * HD + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + r * ROW + ch * 8) = v;
+    }
+    __syncthreads();
+    unsigned qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+        ldmatrix_x4(qf[ks], Qs + (lane & 15) * ROW + ks * 16 + (lane >> 4) * 8);
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const int kw0 = warp * 16;                                // this warp's 16 keys of every tile
+
+    for (int t = t_begin; t < t_end; ++t) {
+        const int buf = (t - t_begin) & 1;
+        bf16* Ks = KVs + buf * 2 * KT * ROW;
+        bf16* Vs = Ks + KT * ROW;
+        if (t + 1 < t_end) {
+            bf16* Kn = KVs + (buf ^ 1) * 2 * KT * ROW;
+            load_kv_tile(Kn, Kn + KT * ROW, cache, bt, (t + 1) * KT, lo, kvl, Hkv, kvh, page_size);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (t * KT + kw0 < kvl) {                             // the warp's keys are not all past the end
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                unsigned kf[4];
+                ldmatrix_x4(kf, Ks + (kw0 + (lane & 7) + (lane >> 4) * 8) * ROW + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16(s[0], qf[ks], kf[0], kf[1]);
+                mma_bf16(s[1], qf[ks], kf[2], kf[3]);
+            }
+            const int key0 = t * KT + kw0 + (lane & 3) * 2;
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + n * 8 + (e & 1);
+                    s[n][e] = (key >= lo && key < kvl) ? s[n][e] * scale_log2 : -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+                }
+            float alpha[2], muse[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                const float mnew = fmaxf(m[i], mx[i]);
+                muse[i] = mnew == -INFINITY ? 0.f : mnew;
+                alpha[i] = exp2f(m[i] - muse[i]);
+                m[i] = mnew;
+                l[i] *= alpha[i];
+            }
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+                o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    s[n][e] = exp2f(s[n][e] - muse[e >> 1]);
+                    l[e >> 1] += s[n][e];
+                }
+            unsigned pa[4];
+            pa[0] = pack_bf16(s[0][0], s[0][1]);
+            pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]);
+            pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                unsigned vf[4];
+                ldmatrix_x4_trans(vf, Vs + (kw0 + (lane & 15)) * ROW + np * 16 + (lane >> 4) * 8);
+                mma_bf16(o[2 * np], pa, vf[0], vf[1]);
+                mma_bf16(o[2 * np + 1], pa, vf[2], vf[3]);
+            }
+        }
+        __syncthreads();
+    }
+
+    // merge the four warps' states through shared memory (the K/V buffers are free now)
+    float* Os = reinterpret_cast<float*>(KVs);               // [4][16][HD]
+    float* Ms = Os + 4 * 16 * HD;                            // [4][16]
+    float* Ls = Ms + 64;                                     // [4][16]
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+        const int r = (lane >> 2) + 8 * i;
+        float* orow = Os + ((size_t)warp * 16 + r) * HD + (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+            orow[n * 8] = o[n][2 * i];
+            orow[n * 8 + 1] = o[n][2 * i + 1];
+        }
+        if ((lane & 3) == 0) {
+            Ms[warp * 16 + r] = m[i];
+            Ls[warp * 16 + r] = l[i];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nheads * HD; idx += THREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, Ms[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(Ms[w * 16 + r] - M);
+                L += Ls[w * 16 + r] * f;
+                O += Os[((size_t)w * 16 + r) * HD + d] * f;
+            }
+        }
+        const int head = head0 + r;
+        const float val = L > 0.f ? O / L : 0.f;
+        if (splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(val);
+        } else {
+            const size_t p = ((size_t)slot * Hq + head) * splits + split;
+            part_o[p * HD + d] = val;
+            if (d == 0) part_lse[p] = L > 0.f ? M + log2f(L) : -INFINITY;
+        }
+    }
+}
+
+// out[token, head, :] = sum_s w_s * part_o[s] / sum_s w_s, w_s = 2^(lse_s - max lse)
+__global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                               bf16* __restrict__ out, int out_stride, const int* __restrict__ cu_q,
+                               const int* __restrict__ entry_list, int Hq, int splits) {
+    const int slot = blockIdx.x, head = blockIdx.y;
+    const int b = entry_list ? entry_list[slot] : slot;
+    if (b < 0) return;
+    const int tok = cu_q[b + 1] - 1;
+    const size_t p = ((size_t)slot * Hq + head) * splits;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_lse[p + s]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float W = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+            for (int s = 0; s < splits; ++s) {
+                const float w = exp2f(part_lse[p + s] - M);
+                W += w;
+                O += w * part_o[(p + s) * HD + d];
+            }
+        }
+        out[(size_t)tok * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(W > 0.f ? O / W : 0.f);
+    }
+}
+
+constexpr size_t PREFILL_SMEM = ((size_t)MT * ROW + 4 * (size_t)KT * ROW) * sizeof(bf16);
+constexpr size_t DECODE_SMEM_KV = 4 * (size_t)KT * ROW * sizeof(bf16);
+constexpr size_t DECODE_SMEM_MERGE = (4 * 16 * (size_t)HD + 128) * sizeof(float);
+constexpr size_t DECODE_SMEM = 16 * (size_t)ROW * sizeof(bf16) +
+                               (DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE);
+
+int configure() {
+    static int status = -1;
+    if (status < 0) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)PREFILL_SMEM);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        status = (int)e;
+    }
+    return status;
+}
+}  // namespace
+
+RI_API int ri_attention_mma_head_dim() { return HD; }
+
+// Tokens per prefill tile for a model with `group` q heads per kv head: 64 rows hold
+// 64 / min(group, 64) tokens of min(group, 64) heads each.
+RI_API int ri_attention_mma_tokens_per_tile(int group) {
+    const int gc = group < MT ? group : MT;
+    return MT / gc;
+}
+
+RI_API int ri_attention_prefill_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                     const void* cache, const int* block_table, int table_stride,
+                                     const int* cu_q, const int* kv_len, const int* tile_entry,
+                                     const int* tile_tok0, int n_tiles, int Hq, int Hkv, int page_size,
+                                     float scale, int window, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv != 0) return (int)cudaErrorInvalidValue;
+    int st = configure();
+    if (st != 0) return st;
+    const int G = Hq / Hkv, Gc = G < MT ? G : MT, chunks = (G + Gc - 1) / Gc, tpt = MT / Gc;
+    dim3 grid(n_tiles, Hkv * chunks);
+    prefill_kernel<<<grid, THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
+        cu_q, kv_len, tile_entry, tile_tok0, Hq, Hkv, Gc, chunks, tpt, page_size,
+        scale * 1.4426950408889634f, window);
+    return ri_launch_status();
+}
+
+// Scratch for `splits` > 1: part_o holds entries*Hq*splits*HD floats, part_lse entries*Hq*splits.
+RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
+                                    const void* cache, const int* block_table, int table_stride,
+                                    const int* cu_q, const int* kv_len, const int* entry_list,
+                                    int n_entries, int Hq, int Hkv, int page_size, float scale, int window,
+                                    int splits, float* part_o, float* part_lse, void* stream) {
+    if (n_entries <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv != 0 || splits < 1 || (splits > 1 && (!part_o || !part_lse)))
+        return (int)cudaErrorInvalidValue;
+    int st = configure();
+    if (st != 0) return st;
+    const int G = Hq / Hkv, Gc = G < 16 ? G : 16, chunks = (G + Gc - 1) / Gc;
+    dim3 grid(Hkv * chunks, splits, n_entries);
+    cudaStream_t s = (cudaStream_t)stream;
+    decode_kernel<<<grid, THREADS, DECODE_SMEM, s>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
+        cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,
+        splits, part_o, part_lse);
+    st = ri_launch_status();
+    if (st != 0 || splits == 1) return st;
+    combine_kernel<<<dim3(n_entries, Hq), HD < 128 ? 64 : 128, 0, s>>>(
+        part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits);
+    return ri_launch_status();
+}

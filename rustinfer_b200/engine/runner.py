@@ -99,7 +99,9 @@ class ModelRunner:
         self.max_batch_seqs = int(max_batch_seqs)
         self.max_batch_tokens = int(max_batch_tokens)
         self.model = Decoder(self.spec)
-        self.ctx = BuildContext(self.device, self.dtype, self.max_model_len, self.page_size)
+        self.ctx = BuildContext(self.device, self.dtype, self.max_model_len, self.page_size,
+                                max_batch_seqs=self.max_batch_seqs,
+                                num_sms=torch.cuda.get_device_properties(self.device).multi_processor_count)
         self.model.prepare(self.ctx)
         self.model.load(load_weights(model_dir, self.model.param_decls(), self.dtype, self.device))
 
@@ -114,10 +116,11 @@ class ModelRunner:
                                   self.max_batch_seqs)
         self._alloc_storage()
         self.tile_rows = self.model.attention_tile_rows()
+        self.prefill_tile_rows = self.model.prefill_tile_rows()
         cap_t, cap_b = self.max_batch_tokens, self.max_batch_seqs
-        n_ints = 4 * cap_t + 4 * cap_b + 64
+        n_ints = 4 * cap_t + 5 * cap_b + 64
         n_ints += len(paged) * (cap_b * self.max_pages_per_request + cap_t + 16)
-        for r in self.tile_rows:
+        for r in self.tile_rows + self.prefill_tile_rows:
             n_ints += 2 * (cap_t // r + cap_b + 8)
         self._staging = _Staging(n_ints, self.device)
         self.steps_run = 0
@@ -243,8 +246,12 @@ class ModelRunner:
             slot_of_token = page_of_token * ps + positions % ps
             np.maximum(table, 0, out=table)
             sections += [table.reshape(-1), slot_of_token]
-        for r in self.tile_rows:
+        decode_list = np.flatnonzero(q_lens == 1)
+        sections.append(decode_list)
+        for r, skip_decode in [(r, False) for r in self.tile_rows] + [(r, True) for r in self.prefill_tile_rows]:
             n_tiles = (q_lens + r - 1) // r
+            if skip_decode:
+                n_tiles = np.where(q_lens == 1, 0, n_tiles)
             tile_entry = np.repeat(np.arange(B), n_tiles)
             first = np.zeros(B, dtype=np.int64)
             np.cumsum(n_tiles[:-1], out=first[1:])
@@ -268,13 +275,16 @@ class ModelRunner:
         for _ in self.layout.paged_groups():
             table = next(it).view(B, max_blocks)
             groups.append(GroupStep(table, next(it)))
+        decode_entries = next(it)
         tiles = {r: (next(it), next(it)) for r in self.tile_rows}
+        prefill_tiles = {r: (next(it), next(it)) for r in self.prefill_tile_rows}
         host_entries = [HostEntry(e.request_id, int(slots[i]), int(q_lens[i]), int(pos0[i]))
                         for i, e in enumerate(entries)]
         step = StepContext(
             num_tokens=T, num_entries=B, token_ids=views[0], positions=views[1], cu_q=views[2],
             kv_len=views[3], state_slots=views[4], groups=groups, tiles=tiles, entries=host_entries,
-            max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), decode_only=bool((q_lens == 1).all()))
+            max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), decode_only=bool((q_lens == 1).all()),
+            decode_entries=decode_entries, num_decode=int(decode_list.size), prefill_tiles=prefill_tiles)
         return step, (views[5] if rows else None)
 
     # --------------------------------------------------------------------------- step

@@ -60,6 +60,12 @@ class Decoder:
             rows.update(b.mixer.attention_tile_rows)
         return tuple(sorted(rows))
 
+    def prefill_tile_rows(self) -> Tuple[int, ...]:
+        rows = set()
+        for b in self.blocks:
+            rows.update(b.mixer.prefill_tile_rows)
+        return tuple(sorted(rows))
+
     @property
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks)

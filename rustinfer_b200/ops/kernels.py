@@ -142,6 +142,68 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, blo
                                  int(window) if window else 0, stream_ptr()), "attention_plain")
 
 
+def _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim):
+    require_cuda(q, out, cache, block_table, cu_q, kv_len)
+    for t, n in ((block_table, "block_table"), (cu_q, "cu_q"), (kv_len, "kv_len")):
+        _i32(t, n)
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
+        raise KernelError("tensor-core attention takes bfloat16 q, out and cache")
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.stride(0) % 8 or q.data_ptr() % 16 or out.stride(0) % 2:
+        raise KernelError("tensor-core attention: q rows must be 16-byte aligned with unit column stride")
+    _contig(cache, "cache")
+    if cache.dim() != 5 or cache.shape[1] != 2 or cache.shape[2] != num_kv_heads or cache.shape[4] != head_dim:
+        raise KernelError("attention: cache must be [pages, 2, Hkv, page, head_dim]")
+    if num_heads % num_kv_heads:
+        raise KernelError("attention: heads must be a multiple of kv heads")
+
+
+def mma_tokens_per_tile(num_heads: int, num_kv_heads: int) -> int:
+    """Query tokens one prefill CTA of the tensor-core kernel covers for this grouping."""
+    return 64 // min(num_heads // num_kv_heads, 64)
+
+
+def attention_prefill_bf16(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0,
+                           num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                           window: Optional[int]) -> None:
+    """Tiles are (entry, first token) pairs of `mma_tokens_per_tile` tokens each."""
+    _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim)
+    require_cuda(tile_entry, tile_tok0)
+    _i32(tile_entry, "tile_entry"); _i32(tile_tok0, "tile_tok0")
+    lib = L.attention_mma(head_dim)
+    check(lib.ri_attention_prefill_bf16(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), _p(block_table),
+                                        block_table.stride(0), _p(cu_q), _p(kv_len), _p(tile_entry),
+                                        _p(tile_tok0), tile_entry.numel(), num_heads, num_kv_heads,
+                                        cache.shape[3], float(scale), int(window) if window else 0,
+                                        stream_ptr()), "attention_prefill_bf16")
+
+
+def decode_scratch_floats(entries: int, num_heads: int, head_dim: int, splits: int):
+    return entries * num_heads * splits * head_dim, entries * num_heads * splits
+
+
+def attention_decode_bf16(q, out, cache, block_table, cu_q, kv_len, entry_list: Optional[torch.Tensor],
+                          n_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                          window: Optional[int], splits: int, part_o: Optional[torch.Tensor],
+                          part_lse: Optional[torch.Tensor]) -> None:
+    """Entries of one token each (entry_list: their indices, None = 0..n-1); `splits` > 1
+    cuts each entry's keys into that many ranges whose partial results go through
+    part_o / part_lse (fp32 scratch)."""
+    _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim)
+    require_cuda(entry_list, part_o, part_lse)
+    _i32(entry_list, "entry_list")
+    if splits > 1:
+        need_o, need_l = decode_scratch_floats(n_entries, num_heads, head_dim, splits)
+        if part_o is None or part_lse is None or part_o.dtype != torch.float32 or \
+                part_lse.dtype != torch.float32 or part_o.numel() < need_o or part_lse.numel() < need_l:
+            raise KernelError(f"attention_decode: scratch must hold {need_o} and {need_l} fp32")
+    lib = L.attention_mma(head_dim)
+    check(lib.ri_attention_decode_bf16(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), _p(block_table),
+                                       block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list), n_entries,
+                                       num_heads, num_kv_heads, cache.shape[3], float(scale),
+                                       int(window) if window else 0, int(splits), _p(part_o), _p(part_lse),
+                                       stream_ptr()), "attention_decode_bf16")
+
+
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
     require_cuda(logits, out)
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32:

@@ -26,6 +26,9 @@ _SIGNATURES = {
     "ri_gemm_f32": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _P],
     "ri_argmax": [_P, _I, _I, _I, _P, _P],
     "ri_sample": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
+    "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
+    "ri_attention_mma_tokens_per_tile": [_I],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
 }
 
@@ -64,6 +67,25 @@ def attention_plain(head_dim: int) -> ctypes.CDLL:
         raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to 512, "
                           f"got {head_dim}")
     return _load(f"ri_attention_plain_hd{head_dim}", ["attention_plain.cu"], [f"RI_HEAD_DIM={head_dim}"])
+
+
+MMA_MAX_HEAD_DIM = 256
+
+
+def attention_mma(head_dim: int) -> ctypes.CDLL:
+    if head_dim % 16 != 0 or not 16 <= head_dim <= MMA_MAX_HEAD_DIM:
+        raise KernelError(f"the tensor-core attention kernels take head sizes that are multiples of 16 "
+                          f"up to {MMA_MAX_HEAD_DIM}, got {head_dim}")
+    return _load(f"ri_attention_mma_hd{head_dim}", ["attention_mma.cu"], [f"RI_HEAD_DIM={head_dim}"])
+
+
+def build_all(head_dims) -> None:
+    """Compile every library for the given head sizes (the ahead-of-time build check)."""
+    core()
+    for hd in head_dims:
+        attention_plain(hd)
+        if hd <= MMA_MAX_HEAD_DIM:
+            attention_mma(hd)
 
 
 def check(code: int, what: str) -> None:

@@ -11,6 +11,7 @@ from typing import Dict, Optional
 import torch
 
 from ..ops import kernels as K
+from ..ops import library as L
 from .base import (BuildContext, Mixer, PagedKV, PagedLayerCache, ParamDecl, POSITIONS, StepContext,
                    register_mixer)
 from .linear import Linear
@@ -24,7 +25,7 @@ class GQAAttention(Mixer):
     keys or values and reads the cache another layer wrote)."""
 
     graph_safe = True
-    attention_tile_rows = (16,)
+    MAX_SPLITS = 16
 
     def __init__(self, params):
         super().__init__(params)
@@ -58,6 +59,22 @@ class GQAAttention(Mixer):
 
     def prepare(self, ctx: BuildContext) -> None:
         super().prepare(ctx)
+        # bf16 runs on the tensor-core kernels (head sizes up to 256); fp32, and larger heads,
+        # on the plain fp32-arithmetic kernel
+        self.use_mma = ctx.dtype == torch.bfloat16 and self.hd <= L.MMA_MAX_HEAD_DIM
+        if self.use_mma:
+            self.tokens_per_tile = K.mma_tokens_per_tile(self.Hq, self.Hkv)
+            self.attention_tile_rows = ()
+            self.prefill_tile_rows = (self.tokens_per_tile,)
+            key = ("decode_scratch", self.Hq, self.hd)
+            if key not in ctx.shared:
+                no, nl = K.decode_scratch_floats(ctx.max_batch_seqs, self.Hq, self.hd, self.MAX_SPLITS)
+                ctx.shared[key] = (torch.empty(no, dtype=torch.float32, device=ctx.device),
+                                   torch.empty(nl, dtype=torch.float32, device=ctx.device))
+            self.part_o, self.part_lse = ctx.shared[key]
+        else:
+            self.attention_tile_rows = (16,)
+            self.prefill_tile_rows = ()
         if self.position_spec is not None:
             key = ("position", self.position_spec.key(), ctx.max_model_len)
             if key not in ctx.shared:
@@ -90,10 +107,31 @@ class GQAAttention(Mixer):
             raise NotImplementedError("attention without a rotary encoding has no cache-write kernel yet")
         q = qkv[:, : self.Hq * self.hd]
         out = torch.empty((T, self.Hq * self.hd), dtype=self.ctx.dtype, device=x.device)
-        tile_entry, tile_q0 = step.tiles[16]
-        K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
-                          self.Hq, self.Hkv, self.hd, self.scale, self.window)
+        if not self.use_mma:
+            tile_entry, tile_q0 = step.tiles[16]
+            K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
+                              self.Hq, self.Hkv, self.hd, self.scale, self.window)
+            return self.o(out, out_dtype=self.ctx.dtype)
+        if step.num_decode:
+            splits = self._splits(step.num_decode, step.max_kv_len)
+            K.attention_decode_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len,
+                                    step.decode_entries, step.num_decode, self.Hq, self.Hkv, self.hd,
+                                    self.scale, self.window, splits, self.part_o, self.part_lse)
+        tile_entry, tile_tok0 = step.prefill_tiles[self.tokens_per_tile]
+        if tile_entry.numel():
+            K.attention_prefill_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry,
+                                     tile_tok0, self.Hq, self.Hkv, self.hd, self.scale, self.window)
         return self.o(out, out_dtype=self.ctx.dtype)
+
+    def _splits(self, n_decode: int, max_kv_len: int) -> int:
+        """Ranges each decoding request's keys are cut into, so that the grid fills the SMs
+        about twice over; never more ranges than 64-key tiles."""
+        chunks = (self.Hq // self.Hkv + 15) // 16
+        ctas = n_decode * self.Hkv * chunks
+        span = min(max_kv_len, self.window) if self.window else max_kv_len
+        tiles = max(1, (span + 63) // 64)
+        want = -(-2 * self.ctx.num_sms // ctas)
+        return max(1, min(want, tiles, self.MAX_SPLITS))
 
     def _q_only(self, qkv: torch.Tensor) -> torch.Tensor:
         return qkv[:, : self.Hq * self.hd]

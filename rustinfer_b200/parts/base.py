@@ -60,7 +60,9 @@ class BuildContext:
     dtype: torch.dtype                  # activation and cache dtype: bfloat16 or float32
     max_model_len: int                  # positions a request can reach
     page_size: int
-    shared: Dict[Any, Any] = field(default_factory=dict)   # tables shared between layers
+    shared: Dict[Any, Any] = field(default_factory=dict)   # tables and scratch shared between layers
+    max_batch_seqs: int = 64            # most entries a step can bring
+    num_sms: int = 148
 
 
 # ------------------------------------------------------------- per-step information
@@ -91,11 +93,16 @@ class StepContext:
     kv_len: torch.Tensor                # [entries] length after this step
     state_slots: torch.Tensor           # [entries]
     groups: List[GroupStep]
-    tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor]]   # rows per tile -> (tile_entry, tile_q0)
+    tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor]]   # tokens per tile -> (tile_entry, tile_q0), all entries
     entries: List[HostEntry]            # host mirror, for parts that are not graph-safe
     max_q_len: int
-    max_kv_len: int
+    max_kv_len: int                     # an upper bound of kv_len (exact in eager steps)
     decode_only: bool
+    # entries of one token (decoding) and tiles over the other entries, for kernels that
+    # treat the two differently
+    decode_entries: Optional[torch.Tensor] = None          # [num_decode] entry indices
+    num_decode: int = 0
+    prefill_tiles: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
 
 
 @dataclass
@@ -138,7 +145,8 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     graph_safe = True                   # forward reads only device tensors of the step
-    attention_tile_rows: Tuple[int, ...] = ()   # tile lists the step must prepare
+    attention_tile_rows: Tuple[int, ...] = ()   # tile lists over all entries the step must prepare
+    prefill_tile_rows: Tuple[int, ...] = ()     # tile lists over the entries of more than one token
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None

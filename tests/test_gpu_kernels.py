@@ -269,6 +269,102 @@ def test_attention_plain_is_bitwise_cut_invariant():
         assert torch.equal(o, out[start: start + n])
 
 
+# ------------------------------------------------------- tensor-core attention (bf16)
+BF = torch.bfloat16
+MMA_SHAPES = ATT_SHAPES + [(24, 8, 128, 16), (32, 1, 64, 16), (5, 1, 32, 8)]
+
+
+def _mma_tiles(case, tpt, skip_decode):
+    te, tq = [], []
+    for b, n in enumerate(case.q_lens):
+        if skip_decode and n == 1:
+            continue
+        for j in range(0, n, tpt):
+            te.append(b); tq.append(j)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
+    return i32(te), i32(tq)
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page", MMA_SHAPES)
+def test_attention_mma_prefill_ragged(Hq, Hkv, hd, page):
+    kv_lens = [1, 17, 64, 65, 130, 33, 16, 300]
+    q_lens = [1, 17, 1, 2, 41, 33, 1, 129]
+    case = PagedCase(BF, Hq, Hkv, hd, page, kv_lens, q_lens, seed=hd + Hq)
+    out = torch.full_like(case.q_all, float("nan"))
+    tpt = K().mma_tokens_per_tile(Hq, Hkv)
+    te, tq = _mma_tiles(case, tpt, skip_decode=False)
+    scale = 1 / math.sqrt(hd)
+    K().attention_prefill_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                               Hq, Hkv, hd, scale, None)
+    close(out, case.reference(scale), BF)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("Hq,Hkv,hd,page", MMA_SHAPES)
+def test_attention_mma_decode_and_prefill_side_by_side(Hq, Hkv, hd, page, splits):
+    """Single-token entries go through the split-KV decode kernel, the others through the
+    prefill kernel, into one output; lengths sit on and around page and tile edges."""
+    kv_lens = [1, 64, 41, 65, 128, 500, 63, 129, 16]
+    q_lens = [1, 1, 20, 1, 1, 1, 7, 1, 1]
+    case = PagedCase(BF, Hq, Hkv, hd, page, kv_lens, q_lens, seed=hd + splits)
+    out = torch.full_like(case.q_all, float("nan"))
+    dec = [b for b, n in enumerate(q_lens) if n == 1]
+    k = K()
+    no, nl = k.decode_scratch_floats(len(dec), Hq, hd, splits)
+    po = torch.full((no,), float("nan"), device=dev())
+    pl = torch.full((nl,), float("nan"), device=dev())
+    scale = 1 / math.sqrt(hd)
+    k.attention_decode_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len,
+                            torch.tensor(dec, dtype=torch.int32, device=dev()), len(dec), Hq, Hkv, hd, scale,
+                            None, splits, po, pl)
+    te, tq = _mma_tiles(case, k.mma_tokens_per_tile(Hq, Hkv), skip_decode=True)
+    k.attention_prefill_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                             Hq, Hkv, hd, scale, None)
+    close(out, case.reference(scale), BF)
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 40, 100])
+def test_attention_mma_window(window):
+    Hq, Hkv, hd = 4, 2, 32
+    case = PagedCase(BF, Hq, Hkv, hd, 8, [70, 9, 40, 200, 300], [30, 9, 1, 1, 150], seed=window)
+    out = torch.full_like(case.q_all, float("nan"))
+    k = K()
+    te, tq = _mma_tiles(case, k.mma_tokens_per_tile(Hq, Hkv), skip_decode=True)
+    k.attention_prefill_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                             Hq, Hkv, hd, 0.2, window)
+    no, nl = k.decode_scratch_floats(2, Hq, hd, 3)
+    k.attention_decode_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len,
+                            torch.tensor([2, 3], dtype=torch.int32, device=dev()), 2, Hq, Hkv, hd, 0.2, window,
+                            3, torch.empty(no, device=dev()), torch.empty(nl, device=dev()))
+    close(out, case.reference(0.2, window), BF)
+
+
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+def test_attention_mma_finds_one_far_key(kernel):
+    Hq, Hkv, hd, page = 8, 2, 64, 16
+    k = K()
+    for far in (0, 15, 16, 63, 64, 255, 300, 310):
+        case = PagedCase(BF, Hq, Hkv, hd, page, [311], [1], seed=far, poison=True)
+        kk = case.k[0].double()
+        rows = []
+        for h in range(Hq):
+            g = h // (Hq // Hkv)
+            rows.append(kk[far, g] / kk[far, g].norm() * 60.0)
+        case.q_all = torch.cat(rows).to(BF).reshape(1, Hq * hd).to(dev())
+        out = torch.full_like(case.q_all, float("nan"))
+        if kernel == "decode":
+            no, nl = k.decode_scratch_floats(1, Hq, hd, 4)
+            k.attention_decode_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, None, 1,
+                                    Hq, Hkv, hd, 1.0, None, 4, torch.empty(no, device=dev()),
+                                    torch.empty(nl, device=dev()))
+        else:
+            te, tq = _mma_tiles(case, k.mma_tokens_per_tile(Hq, Hkv), skip_decode=False)
+            k.attention_prefill_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                                     Hq, Hkv, hd, 1.0, None)
+        want = torch.cat([case.v[0][far, h // (Hq // Hkv)].double() for h in range(Hq)])
+        assert float((out.double().cpu()[0] - want).abs().max()) < 0.05, far
+
+
 @pytest.mark.parametrize("V", [130, 391, 128256])
 def test_argmax_lowest_index_wins(V):
     torch.manual_seed(5)

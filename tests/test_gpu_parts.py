@@ -25,7 +25,7 @@ def ctx(dtype, max_len=256, page=8):
     return BuildContext(dev(), dtype, max_len, page)
 
 
-def one_sequence_step(T, page, n_groups=1):
+def one_sequence_step(T, page, n_groups=1, prefill_rows=()):
     """A StepContext for one whole sequence of T tokens laid out in pages 3, 4, 5, ..."""
     from rustinfer_b200.parts.base import GroupStep, HostEntry, StepContext
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
@@ -36,7 +36,10 @@ def one_sequence_step(T, page, n_groups=1):
     return StepContext(num_tokens=T, num_entries=1, token_ids=i32([0] * T), positions=i32(list(range(T))),
                        cu_q=i32([0, T]), kv_len=i32([T]), state_slots=i32([0]),
                        groups=[GroupStep(table, slot) for _ in range(n_groups)], tiles=tiles,
-                       entries=[HostEntry("x", 0, T, 0)], max_q_len=T, max_kv_len=T, decode_only=False)
+                       entries=[HostEntry("x", 0, T, 0)], max_q_len=T, max_kv_len=T, decode_only=False,
+                       decode_entries=i32([]), num_decode=0,
+                       prefill_tiles={r: (i32([0] * ((T + r - 1) // r)), i32(list(range(0, T, r))))
+                                      for r in prefill_rows})
 
 
 @pytest.mark.parametrize("dt", DT)
@@ -123,7 +126,8 @@ def test_attention_part(dt, Hq, Hkv, hd, window):
     part.load({n: t.to(dev()) for n, t in w.items()})
     x = torch.randn(T, d).to(dt)
     cache = torch.full((12, 2, Hkv, page, hd), float("nan"), dtype=dt, device=dev())
-    y = part.forward(x.to(dev()), one_sequence_step(T, page), PagedLayerCache(cache, 0, True))
+    y = part.forward(x.to(dev()), one_sequence_step(T, page, prefill_rows=part.prefill_tile_rows),
+                     PagedLayerCache(cache, 0, True))
     xd, wd = x.double(), {n: t.double() for n, t in w.items()}
     f = P.rope_inv_freq(hd, 10000.0, None)
     pos = torch.arange(T)
