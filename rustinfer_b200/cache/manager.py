@@ -66,6 +66,7 @@ class CacheLayout:
 @dataclass
 class _Request:
     slot: int
+    uid: int = 0                                                  # unique per open(), even if the id returns
     length: int = 0
     tables: Dict[int, List[int]] = field(default_factory=dict)     # group -> page per position block (-1: given back)
     first_live: Dict[int, int] = field(default_factory=dict)       # group -> first block still held
@@ -84,6 +85,7 @@ class CacheManager:
             self.pools[g] = PagePool(n)
         self.slots = StateSlots(max_requests)
         self._req: Dict[Any, _Request] = {}
+        self._opened = 0
         self.newly_opened_slots: List[int] = []    # slots whose fixed state must be zeroed before use
 
     # ----------------------------------------------------------------- life of a request
@@ -91,7 +93,9 @@ class CacheManager:
         if request_id in self._req:
             raise KeyError(f"request {request_id!r} is already open")
         slot = self.slots.take()
-        self._req[request_id] = _Request(slot, 0, {g: [] for g in self.pools}, {g: 0 for g in self.pools})
+        self._opened += 1
+        self._req[request_id] = _Request(slot, self._opened, 0, {g: [] for g in self.pools},
+                                         {g: 0 for g in self.pools})
         self.newly_opened_slots.append(slot)
         return slot
 
@@ -103,6 +107,10 @@ class CacheManager:
 
     def slot(self, request_id: Any) -> int:
         return self._req[request_id].slot
+
+    def uid(self, request_id: Any) -> int:
+        """A number no other open() ever got: tells a request from a later one of the same id."""
+        return self._req[request_id].uid
 
     def length(self, request_id: Any) -> int:
         return self._req[request_id].length

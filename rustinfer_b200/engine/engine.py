@@ -35,6 +35,13 @@ class GenerationResult:
 
 
 @dataclass
+class StepOutput:
+    request_id: Any
+    token: int
+    finish_reason: Optional[str]        # None while the request goes on
+
+
+@dataclass
 class EngineStats:
     steps: int = 0
     prompt_tokens: int = 0
@@ -61,6 +68,10 @@ class Engine:
                                   capture_sizes=list(capture_sizes if capture_sizes is not None
                                                      else DEFAULT_CAPTURE_SIZES))
         self.sampler = Sampler(self.runner.device, self.runner.spec.vocab_size, max_batch_seqs)
+        r = self.runner
+        self.scheduler = Scheduler(r.cache, r.max_batch_tokens, r.max_batch_seqs, r.max_model_len,
+                                   chunked_prefill_size, r.spec.eos_token_ids)
+        self._requests: Dict[int, Request] = {}
         self.stats = EngineStats()
         self._next_id = 0
 
@@ -73,6 +84,63 @@ class Engine:
                    mem_fraction_static=cfg.mem_fraction_static, num_blocks=cfg.num_blocks,
                    ignore_eos=cfg.ignore_eos, capture_sizes=cfg.capture_sizes)
 
+    # ------------------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], sampling: Optional[SamplingParams] = None) -> int:
+        """Queue one prompt (token ids on the host); returns the request's id."""
+        p = sampling or SamplingParams()
+        if self.ignore_eos and not p.ignore_eos:
+            p = SamplingParams(**{**p.__dict__, "ignore_eos": True})
+        req = Request(self._next_id, [int(t) for t in prompt], p,
+                      seed=p.seed if p.seed is not None else fresh_seed())
+        self._next_id += 1
+        self.scheduler.add(req)
+        self._requests[req.request_id] = req
+        return req.request_id
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> List[StepOutput]:
+        """One iteration: schedule a batch, run it, sample.  Returns what each request that
+        produced a token in this step got (token ids on the host)."""
+        sched = self.scheduler
+        before = sched.num_preemptions
+        plan = sched.schedule()
+        self.stats.preemptions += sched.num_preemptions - before
+        if not plan.entries:
+            return []
+        entries = []
+        samplers: List[Request] = []
+        for e in plan.entries:
+            seq = e.request.sequence
+            entries.append(StepEntry(e.request.request_id, seq[e.start: e.start + e.count],
+                                     [e.count - 1] if e.samples else []))
+            if e.samples:
+                samplers.append(e.request)
+        t0 = time.perf_counter()
+        logits = self.runner.step(entries, borrow_logits=True)
+        sampled: List[int] = []
+        if samplers:
+            sampled = self.sampler.sample(
+                logits, [q.params for q in samplers], [q.seed for q in samplers],
+                [len(q.prompt) + len(q.output) for q in samplers])
+        self.stats.step_ms.append((time.perf_counter() - t0) * 1e3)
+        self.stats.steps += 1
+        self.stats.prompt_tokens += sum(e.count for e in plan.entries) - sum(
+            1 for e in plan.entries if e.count == 1 and e.request.output)
+        self.stats.generated_tokens += len(sampled)
+        sched.complete_step(plan, sampled)
+        return [StepOutput(q.request_id, t, q.finish_reason) for q, t in zip(samplers, sampled)]
+
+    def abort(self, request_id: int) -> None:
+        """Stop a request wherever it is; its pages and slot are given back."""
+        q = self._requests.pop(request_id)
+        self.scheduler.abort(q)
+
+    def take_finished(self, request_id: int) -> "GenerationResult":
+        q = self._requests.pop(request_id)
+        return GenerationResult(q.request_id, q.prompt, q.output, q.finish_reason or "aborted", q.preemptions)
+
     # ------------------------------------------------------------------------ generate
     def generate(self, prompts: Sequence[Sequence[int]],
                  sampling: Union[SamplingParams, Sequence[SamplingParams], None] = None
@@ -84,47 +152,10 @@ class Engine:
         params = [sampling] * len(prompts) if isinstance(sampling, SamplingParams) else list(sampling)
         if len(params) != len(prompts):
             raise ValueError("one SamplingParams for all prompts, or one per prompt")
-        r = self.runner
-        sched = Scheduler(r.cache, r.max_batch_tokens, r.max_batch_seqs, r.max_model_len,
-                          self.chunked_prefill_size, r.spec.eos_token_ids)
-        requests: List[Request] = []
-        for prompt, p in zip(prompts, params):
-            if self.ignore_eos and not p.ignore_eos:
-                p = SamplingParams(**{**p.__dict__, "ignore_eos": True})
-            req = Request(self._next_id, [int(t) for t in prompt], p,
-                          seed=p.seed if p.seed is not None else fresh_seed())
-            self._next_id += 1
-            sched.add(req)
-            requests.append(req)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         t0 = time.perf_counter()
-        while sched.has_work():
-            plan = sched.schedule()
-            if not plan.entries:
+        while self.scheduler.has_work():
+            if not self.step() and not self.scheduler.has_work():
                 break
-            self._run_plan(sched, plan)
         self.stats.seconds += time.perf_counter() - t0
-        self.stats.preemptions += sched.num_preemptions
-        return [GenerationResult(q.request_id, q.prompt, q.output, q.finish_reason or "aborted",
-                                 q.preemptions) for q in requests]
-
-    def _run_plan(self, sched: Scheduler, plan) -> None:
-        entries = []
-        samplers: List[Request] = []
-        for e in plan.entries:
-            seq = e.request.sequence
-            entries.append(StepEntry(e.request.request_id, seq[e.start: e.start + e.count],
-                                     [e.count - 1] if e.samples else []))
-            if e.samples:
-                samplers.append(e.request)
-        t0 = time.perf_counter()
-        logits = self.runner.step(entries)
-        sampled: List[int] = []
-        if samplers:
-            sampled = self.sampler.sample(
-                logits, [q.params for q in samplers], [q.seed for q in samplers],
-                [len(q.prompt) + len(q.output) for q in samplers])
-        self.stats.step_ms.append((time.perf_counter() - t0) * 1e3)
-        self.stats.steps += 1
-        self.stats.prompt_tokens += sum(e.count for e in plan.entries if not (e.count == 1 and e.request.output))
-        self.stats.generated_tokens += len(sampled)
-        sched.complete_step(plan, sampled)
+        return [self.take_finished(i) for i in ids]

@@ -78,6 +78,126 @@ class _Staging:
         self.events[i] = ev
 
 
+class _DecodeGraph:
+    """A captured step of `bucket` single tokens.  Its index arrays live in one device
+    buffer at fixed addresses; rows beyond the live entries are padding that reads one key
+    of page 0 and writes nothing (RustInfer pads with one-token rows on a scratch block,
+    crates/infer-worker/src/application/worker_scheduler.rs:685-718)."""
+
+    def __init__(self, runner: "ModelRunner", bucket: int):
+        self.bucket = bucket
+        P = runner.max_pages_per_request
+        groups = runner.layout.paged_groups()
+        # fixed layout: token_ids, positions, cu_q, kv_len, slots, rows, [table, slot_of_token]*, decode list, tiles
+        sizes = [bucket, bucket, bucket + 1, bucket, bucket, bucket]
+        for _ in groups:
+            sizes += [bucket * P, bucket]
+        sizes.append(bucket)
+        for _ in runner.tile_rows:
+            sizes += [bucket, bucket]
+        self.offsets = []
+        at = 0
+        for n in sizes:
+            self.offsets.append((at, n))
+            at += (n + 3) & ~3
+        self.host = torch.zeros(at, dtype=torch.int32).pin_memory()
+        self.hv = self.host.numpy()
+        self.dev = torch.zeros(at, dtype=torch.int32, device=runner.device)
+        self.event: Optional[torch.cuda.Event] = None
+        self.row_owner: List[Any] = [None] * bucket          # uid of the request whose table sits in a row
+        self.row_pages: List[List[int]] = [[0] * len(groups) for _ in range(bucket)]
+        v = [self.dev[o: o + n] for o, n in self.offsets]
+        hv = [self.hv[o: o + n] for o, n in self.offsets]
+        self.h_tokens, self.h_pos, h_cu, self.h_kv, self.h_slots, h_rows = hv[:6]
+        h_cu[:] = np.arange(bucket + 1)
+        h_rows[:] = np.arange(bucket)
+        self.h_pos[:] = 0
+        self.h_kv[:] = 1
+        it, hit = iter(v[6:]), iter(hv[6:])
+        gsteps, self.h_tables, self.h_slot_of_token = [], [], []
+        for _ in groups:
+            gsteps.append(GroupStep(next(it).view(bucket, P), next(it)))
+            self.h_tables.append(next(hit).reshape(bucket, P))
+            h = next(hit)
+            h[:] = -1
+            self.h_slot_of_token.append(h)
+        decode_entries = next(it)
+        next(hit)[:] = np.arange(bucket)
+        tiles = {}
+        for r in runner.tile_rows:
+            tiles[r] = (next(it), next(it))
+            next(hit)[:] = np.arange(bucket)
+            next(hit)[:] = 0
+        self.dev.copy_(self.host)
+        self.step = StepContext(
+            num_tokens=bucket, num_entries=bucket, token_ids=v[0], positions=v[1], cu_q=v[2], kv_len=v[3],
+            state_slots=v[4], groups=gsteps, tiles=tiles, entries=[], max_q_len=1,
+            max_kv_len=runner.max_model_len, decode_only=True, decode_entries=decode_entries,
+            num_decode=bucket, prefill_tiles={r: (v[0][:0], v[0][:0]) for r in runner.prefill_tile_rows})
+        self.rows = v[5]
+        # one eager run (libraries pick their algorithms, lazy kernels get built), then capture
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            runner.model.forward(self.step, runner.entry_caches, self.rows)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        from ..ops import library as _lib
+        before = _lib.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=runner._graph_pool):
+            self.logits = runner.model.forward(self.step, runner.entry_caches, self.rows)
+        self.kernels_per_replay = _lib.launch_count - before
+        if runner._graph_pool is None:
+            runner._graph_pool = self.graph.pool()
+
+    def fill(self, runner: "ModelRunner", entries: Sequence[StepEntry], host_tokens: bool) -> None:
+        """Write this step's indices into the pinned buffer and send it.  A row keeps the
+        block table of the request it held last step; only pages added since are written."""
+        if self.event is not None:
+            self.event.synchronize()                         # the last upload has left the host buffer
+        ps = runner.page_size
+        cache = runner.cache
+        groups = runner.layout.paged_groups()
+        for i, e in enumerate(entries):
+            rid = e.request_id
+            pos = cache.length(rid)
+            if host_tokens:
+                self.h_tokens[i] = e.tokens[0]
+            self.h_pos[i] = pos
+            self.h_kv[i] = pos + 1
+            self.h_slots[i] = cache.slot(rid)
+            uid = cache.uid(rid)
+            if self.row_owner[i] != uid:
+                self.row_owner[i] = uid
+                self.row_pages[i] = [0] * len(groups)
+            for gi, g in enumerate(groups):
+                table = cache.block_table(rid, g)
+                start, n = self.row_pages[i][gi], len(table)
+                if start < n:
+                    row = self.h_tables[gi][i]
+                    row[start:n] = table[start:n]
+                    np.maximum(row[start:n], 0, out=row[start:n])
+                    self.row_pages[i][gi] = n
+                page = table[pos // ps]
+                if page < 0:
+                    raise StepError("a token would be written to a page that was given back")
+                self.h_slot_of_token[gi][i] = page * ps + pos % ps
+        for i in range(len(entries), self.bucket):           # padding rows
+            if self.row_owner[i] is not None:
+                self.row_owner[i] = None
+                self.h_pos[i] = 0
+                self.h_kv[i] = 1
+                self.h_tokens[i] = 0
+                for h in self.h_slot_of_token:
+                    h[i] = -1
+        self.dev.copy_(self.host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.event = ev
+
+
 class ModelRunner:
     """Model, cache and step function of one model folder on one GPU."""
 
@@ -124,6 +244,11 @@ class ModelRunner:
             n_ints += 2 * (cap_t // r + cap_b + 8)
         self._staging = _Staging(n_ints, self.device)
         self.steps_run = 0
+        self.h2d_bytes_last = 0
+        self.graph_replays = 0
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graph_pool = None
+        self.use_graphs = bool(self.capture_sizes) and self.model.graph_safe
 
     # ------------------------------------------------------------------------ storage
     def _auto_pages(self, fraction: float) -> int:
@@ -268,6 +393,7 @@ class ModelRunner:
             offsets.append((at, n))
             at += (n + 3) & ~3                      # every section starts on a 16-byte boundary
         self._staging.upload(idx, at)
+        self.h2d_bytes_last = at * 4
         dev = self._staging.dev
         views = [dev[o: o + n] for o, n in offsets]
         it = iter(views[6:])
@@ -288,19 +414,67 @@ class ModelRunner:
         return step, (views[5] if rows else None)
 
     # --------------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None,
+             borrow_logits: bool = False) -> Optional[torch.Tensor]:
         """Run one batch.  Returns fp32 logits [wanted, vocab] on the device in the order of
         the entries and of their `want`, or None when nothing is wanted.  Raises `OutOfPages`
-        before anything runs if the cache cannot hold the new tokens (nothing is changed)."""
+        before anything runs if the cache cannot hold the new tokens (nothing is changed).
+
+        `device_tokens` (int32 on the device, one per entry) replaces the entries' token ids
+        in a step of single tokens: the ids chosen by the last step need not visit the host
+        before they are fed back.  With `borrow_logits` the result may be a view of a buffer
+        that the next step overwrites (for callers that consume it at once)."""
         self._validate(entries)
         self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
         self._zero_new_state()
-        step, rows = self._build(entries)
-        logits = self.model.forward(step, self.entry_caches, rows)
+        bucket = self._bucket_for(entries)
+        if bucket:
+            logits = self._graph_step(entries, bucket, device_tokens)
+            if logits is not None and not borrow_logits:
+                logits = logits.clone()
+        else:
+            step, rows = self._build(entries)
+            if device_tokens is not None:
+                if not step.decode_only:
+                    raise StepError("device_tokens only stands for steps of single tokens")
+                step.token_ids[: step.num_tokens].copy_(device_tokens[: step.num_tokens])
+            logits = self.model.forward(step, self.entry_caches, rows)
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # ------------------------------------------------------------------ decode graphs
+    def _bucket_for(self, entries: Sequence[StepEntry]) -> int:
+        """Smallest captured batch size that holds a step of single tokens, else 0
+        (crates/infer-worker/src/application/runtime/graph_exec.rs:98-134)."""
+        if not self.use_graphs or any(len(e.tokens) != 1 for e in entries):
+            return 0
+        for c in self.capture_sizes:
+            if c >= len(entries):
+                return c if c <= self.max_batch_seqs else 0
+        return 0
+
+    def _graph_step(self, entries: Sequence[StepEntry], bucket: int,
+                    device_tokens: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = _DecodeGraph(self, bucket)
+            self._graphs[bucket] = g
+        g.fill(self, entries, device_tokens is None)
+        if device_tokens is not None:
+            g.step.token_ids[: len(entries)].copy_(device_tokens[: len(entries)])
+        g.graph.replay()
+        self.graph_replays += 1
+        self.h2d_bytes_last = g.host.numel() * 4
+        from ..ops import library as _lib
+        _lib.launch_count += g.kernels_per_replay
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if not wanted:
+            return None
+        if len(wanted) == len(entries):
+            return g.logits[: len(entries)]
+        return g.logits[torch.tensor(wanted, device=self.device)]
 
     def _zero_new_state(self) -> None:
         new = self.cache.newly_opened_slots

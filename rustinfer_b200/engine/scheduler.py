@@ -102,6 +102,13 @@ class Scheduler:
                              f"no room under max_model_len {self.max_model_len}")
         self.waiting.append(request)
 
+    def abort(self, request: Request) -> None:
+        if request in self.waiting:
+            self.waiting.remove(request)
+            request.state, request.finish_reason = FINISHED, "aborted"
+        elif request in self.running:
+            self._fail(request, "aborted")
+
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 

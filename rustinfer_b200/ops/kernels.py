@@ -201,7 +201,7 @@ def attention_decode_bf16(q, out, cache, block_table, cu_q, kv_len, entry_list: 
                                        block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list), n_entries,
                                        num_heads, num_kv_heads, cache.shape[3], float(scale),
                                        int(window) if window else 0, int(splits), _p(part_o), _p(part_lse),
-                                       stream_ptr()), "attention_decode_bf16")
+                                       stream_ptr()), "attention_decode_bf16", 2 if splits > 1 else 1)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

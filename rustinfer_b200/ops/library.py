@@ -88,7 +88,12 @@ def build_all(head_dims) -> None:
             attention_mma(hd)
 
 
-def check(code: int, what: str) -> None:
+launch_count = 0        # kernels of this package launched (or captured into a graph) so far
+
+
+def check(code: int, what: str, launches: int = 1) -> None:
+    global launch_count
+    launch_count += launches
     if code != 0:
         lib = core()
         lib.ri_error_string.restype = ctypes.c_char_p

@@ -290,3 +290,60 @@ def test_preemption_recomputes_to_the_same_tokens(models):
     b = tight.generate(prompts, sp)
     assert tight.stats.preemptions > 0 and roomy.stats.preemptions == 0
     assert [x.tokens for x in a] == [x.tokens for x in b]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_graphs_equal_eager_steps(models, dtype):
+    """Steps of single tokens replayed from a captured graph give the logits of the eager
+    step: with rows that change owner, padding rows, a request id that returns with other
+    pages, and token ids fed back on the device."""
+    from rustinfer_b200.engine.runner import ModelRunner, StepEntry
+    folder, plain = models["B"]
+    V = TINY["B"]["vocab_size"]
+    mk = lambda sizes: ModelRunner(folder, dtype=dtype, max_model_len=128, page_size=8, num_pages=48,
+                                   max_batch_seqs=4, max_batch_tokens=128, capture_sizes=sizes)
+    eager, graph = mk(None), mk([1, 2, 4])
+    assert not eager.use_graphs and graph.use_graphs
+    seqs = {i: random_ids(40 + 7 * i, V, 200 + i) for i in range(5)}
+    for r in (eager, graph):
+        r.got = {i: [] for i in seqs}
+        for i in (0, 1, 2):
+            r.open(i)
+            r.got[i].append(r.step([StepEntry(i, seqs[i][:9 + i], list(range(9 + i)))]))
+    at = {0: 9, 1: 10, 2: 11}
+    live = [0, 1, 2]
+    nxt = 3
+    for turn in range(2000):
+        if not live:
+            break
+        batch = [i for i in live if (turn + i) % 4 != 3] or live[:1]      # 1 to 3 rows: buckets 1, 2, 4
+        for r in (eager, graph):
+            lg = r.step([StepEntry(i, [seqs[i][at[i]]], [0]) for i in batch])
+            for k, i in enumerate(batch):
+                r.got[i].append(lg[k: k + 1])
+        for i in batch:
+            at[i] += 1
+            if at[i] == len(seqs[i]):
+                live.remove(i)
+                for r in (eager, graph):
+                    r.close(i)
+                if nxt < 5:                                               # a new request takes the row
+                    for r in (eager, graph):
+                        r.open(nxt)
+                        r.got[nxt].append(r.step([StepEntry(nxt, seqs[nxt][:5], list(range(5)))]))
+                    at[nxt] = 5
+                    live.append(nxt)
+                    nxt += 1
+    assert graph.graph_replays > 50 and sorted(graph._graphs) == [1, 2, 4]
+    for i in seqs:
+        e, g = torch.cat(eager.got[i]), torch.cat(graph.got[i])
+        assert rel_err(g, plain.logits(seqs[i])) <= TOL[dtype]
+        if dtype == "float32":
+            assert torch.equal(e, g)
+    # the same id again, on other pages, with device-fed tokens
+    graph.open(0), graph.open(99)
+    graph.step([StepEntry(99, seqs[1][:20], [])])
+    graph.step([StepEntry(0, seqs[0][:6], [])])
+    toks = torch.tensor(seqs[0][6:12], dtype=torch.int32, device="cuda:0")
+    outs = [graph.step([StepEntry(0, [0], [0])], device_tokens=toks[k: k + 1]) .clone() for k in range(6)]
+    assert rel_err(torch.cat(outs), plain.logits(seqs[0])[6:12]) <= TOL[dtype]
