@@ -518,3 +518,87 @@ RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int 
         part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits);
     return ri_launch_status();
 }
+
+// ===================================================== decode without an allocator
+// See attention_decode_static.h: the same two kernels as ri_attention_decode_bf16, with
+// the split partials in an array that lives inside this library.
+#include "attention_decode_static.h"
+#include <stdio.h>
+
+namespace {
+static __device__ __align__(256) float g_decode_static_scratch[RI_DECODE_STATIC_SCRATCH_FLOATS];
+
+constexpr int MAX_DEVICES = 64;
+// Device address of the array per device; in host code the array's name is only a handle
+// for cudaGetSymbolAddress, never a pointer a kernel could be given.
+float* g_decode_static_ptr[MAX_DEVICES] = {nullptr};
+thread_local char g_decode_static_msg[256] = "";
+
+int decode_static_setup(int device, float** ptr) {
+    if (g_decode_static_ptr[device] == nullptr) {
+        float* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);
+        if (e != cudaSuccess) {
+            snprintf(g_decode_static_msg, sizeof g_decode_static_msg,
+                     "cudaGetSymbolAddress for the static scratch failed: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+        if (e != cudaSuccess) {
+            snprintf(g_decode_static_msg, sizeof g_decode_static_msg,
+                     "raising the decode kernel's shared-memory limit failed: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        g_decode_static_ptr[device] = p;
+    }
+    *ptr = g_decode_static_ptr[device];
+    return 0;
+}
+}  // namespace
+
+const char* ri_attention_decode_static_error(void) { return g_decode_static_msg; }
+
+int ri_attention_decode_bf16_static(const void* q, int q_stride, void* out, int out_stride,
+                                    const void* cache, const int* block_table, int table_stride,
+                                    const int* cu_q, const int* kv_len, const int* entry_list,
+                                    int n_entries, int Hq, int Hkv, int page_size, float scale,
+                                    int window, int splits, void* stream) {
+    g_decode_static_msg[0] = 0;
+    if (n_entries <= 0) return 0;
+    if (Hkv <= 0 || Hq % Hkv != 0 || splits < 1) {
+        snprintf(g_decode_static_msg, sizeof g_decode_static_msg,
+                 "bad sizes: q heads %d, kv heads %d, splits %d", Hq, Hkv, splits);
+        return (int)cudaErrorInvalidValue;
+    }
+    const long long need = (long long)n_entries * Hq * splits * (HD + 1);
+    if (need > (long long)RI_DECODE_STATIC_SCRATCH_FLOATS) {
+        snprintf(g_decode_static_msg, sizeof g_decode_static_msg,
+                 "entries %d x q heads %d x splits %d x (head_dim %d + 1) = %lld floats exceed the static "
+                 "scratch of %d floats; use fewer splits or entries, or ri_attention_decode_bf16 with "
+                 "scratch of your own", n_entries, Hq, splits, HD, need, RI_DECODE_STATIC_SCRATCH_FLOATS);
+        return (int)cudaErrorInvalidValue;
+    }
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+        snprintf(g_decode_static_msg, sizeof g_decode_static_msg, "no usable current device (%d)", device);
+        return (int)(e != cudaSuccess ? e : cudaErrorInvalidDevice);
+    }
+    float* scratch = nullptr;
+    int st = decode_static_setup(device, &scratch);
+    if (st != 0) return st;
+    float* part_o = scratch;                                               // [entries][Hq][splits][HD]
+    float* part_lse = scratch + (size_t)n_entries * Hq * splits * HD;      // [entries][Hq][splits]
+    const int G = Hq / Hkv, Gc = G < 16 ? G : 16, chunks = (G + Gc - 1) / Gc;
+    dim3 grid(Hkv * chunks, splits, n_entries);
+    cudaStream_t s = (cudaStream_t)stream;
+    decode_kernel<<<grid, THREADS, DECODE_SMEM, s>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
+        cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,
+        splits, part_o, part_lse);
+    st = ri_launch_status();
+    if (st != 0 || splits == 1) return st;
+    combine_kernel<<<dim3(n_entries, Hq), HD < 128 ? 64 : 128, 0, s>>>(
+        part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits);
+    return ri_launch_status();
+}
