@@ -123,13 +123,13 @@ def fill_context(engine, batch, ctx0, vocab, seed):
     return ids
 
 
-def decode_device_timed(engine, batch, steps, warmup, vocab, seed):
-    """K decode steps of `batch` requests that end at CONTEXT tokens; device time."""
+def decode_device_timed(engine, batch, steps, warmup, vocab, seed, context=CONTEXT):
+    """K decode steps of `batch` requests that end at `context` tokens; device time."""
     import torch
     from rustinfer_b200.engine.runner import StepEntry
     from rustinfer_b200.ops import library
     r = engine.runner
-    ctx0 = CONTEXT - (steps + warmup)
+    ctx0 = context - (steps + warmup)
     ids = fill_context(engine, batch, ctx0, vocab, seed)
     tokens = torch.randint(0, vocab, (batch,), dtype=torch.int32, device=r.device)
     entries = [StepEntry(rid, [0], [0]) for rid in ids]
@@ -232,6 +232,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                     help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"],
+                    help="run one part alone and print its time (for profiler captures; no JSON line)")
+    ap.add_argument("--eager", action="store_true", help="with --only decode: no CUDA graphs")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: --gpus {args.gpus} is not supported by this engine")
@@ -257,6 +261,20 @@ def main() -> int:
     windows = []
     with tempfile.TemporaryDirectory(prefix="rustinfer_b200_bench_") as tmp:
         folder = write_random_model(os.path.join(tmp, "model"), cfg, seed=SEED, std=STD)
+        if args.only:
+            seqs = max(args.batch, 1)
+            engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=seqs,
+                            max_model_len=CONTEXT, paged_block_size=PAGE, num_blocks=seqs * CONTEXT // PAGE + 64,
+                            capture_sizes=[] if args.eager else [1, 2, 4, 8, 16, 32, 64], ignore_eos=True)
+            if args.only == "decode":
+                global_ctx = args.context
+                ms, n, _ = decode_device_timed(engine, args.batch, args.steps, args.warmup, vocab, 1, global_ctx)
+                print(f"decode b{args.batch} ctx{global_ctx} layers{args.layers}: {ms:.4f} ms/step, {n} launches")
+            else:
+                ms, _ = prefill_timed(engine, vocab, PREFILL_TOKENS, repeats=max(1, min(args.steps, 3)))
+                print(f"prefill {PREFILL_TOKENS} layers{args.layers}: {ms:.3f} ms")
+            clocks.stop()
+            return 0
         engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=64,
                         max_model_len=CONTEXT, paged_block_size=PAGE, chunked_prefill_size=0,
                         num_blocks=64 * CONTEXT // PAGE + 64, capture_sizes=[1, 2, 4, 8, 16, 32, 64],
