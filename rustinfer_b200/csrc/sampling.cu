@@ -25,12 +25,18 @@ __device__ __forceinline__ float from_ordered(unsigned int k) {
 }
 
 // ------------------------------------------------------------------------- argmax
-__global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
-    __shared__ unsigned long long best[32];
-    const float* row = logits + (size_t)blockIdx.x * ld;
+// grid (blocks per row, rows).  Every CTA reduces its slice of a row to a 64-bit key
+// (ordered logit, ~index), merges it into state[row] with atomicMax, and the CTA that
+// arrives last writes the token and puts state and counter back to zero, so the scratch
+// is ready for the next call without a memset.  `state` and `count` start as zeros.
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
+              unsigned long long* __restrict__ state, unsigned int* __restrict__ count) {
+    __shared__ unsigned long long best[8];
+    const int row_id = blockIdx.y;
+    const float* row = logits + (size_t)row_id * ld;
     unsigned long long mine = 0ull;                      // (ordered logit << 32) | ~index
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
         const unsigned long long key =
             ((unsigned long long)ordered_bits(row[i]) << 32) | (unsigned int)(0xffffffffu - (unsigned int)i);
         mine = key > mine ? key : mine;
@@ -42,14 +48,17 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
     }
     if ((threadIdx.x & 31) == 0) best[threadIdx.x >> 5] = mine;
     __syncthreads();
-    if (threadIdx.x < 32) {
-        mine = threadIdx.x < ((blockDim.x + 31) >> 5) ? best[threadIdx.x] : 0ull;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xffffffffu, mine, o);
-            mine = other > mine ? other : mine;
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (int)(blockDim.x >> 5); ++w) mine = best[w] > mine ? best[w] : mine;
+        atomicMax(&state[row_id], mine);
+        __threadfence();
+        const unsigned int ticket = atomicAdd(&count[row_id], 1u);
+        if (ticket == gridDim.x - 1) {
+            __threadfence();
+            const unsigned long long top = atomicExch(&state[row_id], 0ull);
+            out[row_id] = (int)(0xffffffffu - (unsigned int)(top & 0xffffffffu));
+            count[row_id] = 0u;
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = (int)(0xffffffffu - (unsigned int)(mine & 0xffffffffu));
     }
 }
 
@@ -170,10 +179,16 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, int vpad,
 }
 }  // namespace
 
-RI_API int ri_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* stream) {
+// state: rows 64-bit words, count: rows 32-bit words, both zero before the first call (the
+// kernel leaves them zero).  Calls that share them must not overlap on the GPU.
+RI_API int ri_argmax(const float* logits, int ld, int rows, int vocab, int* out,
+                     unsigned long long* state, unsigned int* count, void* stream) {
     if (rows <= 0) return 0;
-    const int threads = vocab >= 4096 ? 1024 : 256;
-    argmax_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
+    int per_row = (vocab + 2047) / 2048;                 // 8 elements per thread
+    const int cap = (4 * 148 + rows - 1) / rows;         // about four CTAs per SM in all
+    if (per_row > cap) per_row = cap;
+    if (per_row < 1) per_row = 1;
+    argmax_kernel<<<dim3(per_row, rows), 256, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out, state, count);
     return ri_launch_status();
 }
 

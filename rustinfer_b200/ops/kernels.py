@@ -204,11 +204,31 @@ def attention_decode_bf16(q, out, cache, block_table, cu_q, kv_len, entry_list: 
                                        stream_ptr()), "attention_decode_bf16", 2 if splits > 1 else 1)
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
-    require_cuda(logits, out)
+_argmax_state = {}
+
+
+def argmax_state(device: torch.device, rows: int) -> torch.Tensor:
+    """Zeroed scratch of the argmax kernel for up to `rows` rows: int64 [2 * rows], the
+    merged keys followed by the arrival counters.  The kernel leaves it zero."""
+    return torch.zeros(2 * rows, dtype=torch.int64, device=device)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, state: Optional[torch.Tensor] = None) -> None:
+    """out[r] = index of the largest logit of row r, the lowest index among equals."""
+    require_cuda(logits, out, state)
     if logits.dtype != torch.float32 or logits.stride(1) != 1 or out.dtype != torch.int32:
         raise KernelError("argmax: logits fp32 [R,V], out int32 [R]")
-    check(L.core().ri_argmax(_p(logits), logits.stride(0), logits.shape[0], logits.shape[1], _p(out),
+    R = logits.shape[0]
+    if state is None:
+        key = (logits.device, torch.cuda.current_stream().cuda_stream)
+        state = _argmax_state.get(key)
+        if state is None or state.numel() < 2 * R:
+            state = argmax_state(logits.device, max(R, 64))
+            _argmax_state[key] = state
+    if state.dtype != torch.int64 or state.numel() < 2 * R:
+        raise KernelError(f"argmax: state must be int64 [{2 * R}]")
+    check(L.core().ri_argmax(_p(logits), logits.stride(0), R, logits.shape[1], _p(out),
+                             state.data_ptr(), state.data_ptr() + 8 * (state.numel() // 2),
                              stream_ptr()), "argmax")
 
 

@@ -45,11 +45,12 @@ class Sampler:
         self.vocab = vocab_size
         self.max_rows = max_rows
         self._out = torch.empty(max_rows, dtype=torch.int32, device=device)
+        self._argmax_state = K.argmax_state(device, max_rows)
         self._scratch: Optional[torch.Tensor] = None
 
     def argmax_device(self, logits: torch.Tensor) -> torch.Tensor:
         out = self._out[: logits.shape[0]]
-        K.argmax(logits, out)
+        K.argmax(logits, out, self._argmax_state)
         return out
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
