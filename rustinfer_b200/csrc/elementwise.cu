@@ -72,11 +72,91 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
     }
 }
 
+// bf16 activations, width a multiple of 8 and at most 8 * 1024: every thread keeps its 8
+// elements in registers between the sum of squares and the scaling, and moves 16 or 32
+// bytes per access.
+__device__ __forceinline__ void bf16x8_to_float(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(p[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 float_to_bf16x8(const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
+template <typename TW>
+__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const bf16* __restrict__ delta,
+                                          const TW* __restrict__ w, float eps, bf16* __restrict__ out,
+                                          const int* __restrict__ rows, int d) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const int i0 = threadIdx.x * 8;
+    const bool active = i0 < d;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    float ss = 0.f;
+    if (active) {
+        float* hp = h + (size_t)src * d + i0;
+        const float4 a = *reinterpret_cast<const float4*>(hp);
+        const float4 b = *reinterpret_cast<const float4*>(hp + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        if (delta) {
+            float dv[8];
+            bf16x8_to_float(*reinterpret_cast<const uint4*>(delta + (size_t)src * d + i0), dv);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] += dv[i];
+            if (!rows) {
+                *reinterpret_cast<float4*>(hp) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4*>(hp + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    }
+    ss = block_sum(ss, red);
+    if (!active) return;
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    float wv[8];
+    if (sizeof(TW) == 2) {
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(w) + i0), wv);
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i0);
+        const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i0 + 4);
+        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * wv[i];
+    *reinterpret_cast<uint4*>(out + (size_t)r * d + i0) = float_to_bf16x8(v);
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 RI_API int ri_add_rmsnorm(float* h, const void* delta, const void* w, int w_dtype, float eps,
                           void* out, int act_dtype, const int* rows, int n_rows, int d,
                           void* stream) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == RI_BF16 && d % 8 == 0 && d <= 8192 && aligned16(h) && aligned16(out) && aligned16(w) &&
+        (!delta || aligned16(delta))) {
+        const int vt = ((d / 8 + 31) / 32) * 32;
+        if (w_dtype == RI_BF16)
+            add_rmsnorm_bf16x8_kernel<bf16><<<n_rows, vt, 0, s>>>(h, (const bf16*)delta, (const bf16*)w, eps,
+                                                                  (bf16*)out, rows, d);
+        else
+            add_rmsnorm_bf16x8_kernel<float><<<n_rows, vt, 0, s>>>(h, (const bf16*)delta, (const float*)w, eps,
+                                                                   (bf16*)out, rows, d);
+        return ri_launch_status();
+    }
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
 #define RI_LAUNCH(TA, TW)                                                                  \
     add_rmsnorm_kernel<TA, TW><<<n_rows, threads, 0, s>>>(h, (const TA*)delta, (const TW*)w, \
@@ -166,6 +246,68 @@ __global__ void rope_scatter_kernel(TA* __restrict__ qkv, int row_stride,
     }
 }
 
+// bf16, head_dim and rotary_dim multiples of 16: one work item = 8 elements of the first
+// half of a head and their 8 partners, or 8 elements that are only copied.
+__global__ void rope_scatter_bf16x8_kernel(bf16* __restrict__ qkv, int row_stride,
+                                           const int* __restrict__ positions,
+                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                           const int* __restrict__ slot_of_token, bf16* __restrict__ cache,
+                                           int Hq, int Hkv, int hd, int rot, int page_size) {
+    const int t = blockIdx.x;
+    const int half = rot >> 1;
+    const int pos = positions[t];
+    bf16* row = qkv + (size_t)t * row_stride;
+    const float* ct = cos_t + (size_t)pos * half;
+    const float* st = sin_t + (size_t)pos * half;
+    const int slot = (slot_of_token && Hkv > 0) ? slot_of_token[t] : -1;
+    bf16* kdst = nullptr;
+    bf16* vdst = nullptr;
+    if (slot >= 0) {
+        const int page = slot / page_size, off = slot - page * page_size;
+        kdst = cache + ((size_t)(page * 2 + 0) * Hkv * page_size + off) * hd;
+        vdst = cache + ((size_t)(page * 2 + 1) * Hkv * page_size + off) * hd;
+    }
+    const size_t head_step = (size_t)page_size * hd;
+    const int vph = half >> 3;                               // rotating vectors per head
+    const int n_rot = (Hq + Hkv) * vph;
+    for (int wi = threadIdx.x; wi < n_rot; wi += blockDim.x) {
+        const int head = wi / vph, i = (wi - head * vph) * 8;
+        if (head >= Hq && !kdst) continue;
+        bf16* p = row + (size_t)head * hd;
+        float x1[8], x2[8], c[8], s[8];
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(p + i), x1);
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(p + i + half), x2);
+        *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(ct + i);
+        *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(ct + i + 4);
+        *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(st + i);
+        *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(st + i + 4);
+        float y1[8], y2[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            y1[k] = x1[k] * c[k] - x2[k] * s[k];
+            y2[k] = x1[k] * s[k] + x2[k] * c[k];
+        }
+        bf16* dst = head < Hq ? p : kdst + (size_t)(head - Hq) * head_step;
+        *reinterpret_cast<uint4*>(dst + i) = float_to_bf16x8(y1);
+        *reinterpret_cast<uint4*>(dst + i + half) = float_to_bf16x8(y2);
+    }
+    if (kdst) {
+        const int pass_v = (hd - rot) >> 3;                  // unrotated tail of each k head
+        for (int wi = threadIdx.x; wi < Hkv * pass_v; wi += blockDim.x) {
+            const int g = wi / pass_v, i = rot + (wi - g * pass_v) * 8;
+            *reinterpret_cast<uint4*>(kdst + (size_t)g * head_step + i) =
+                *reinterpret_cast<const uint4*>(row + (size_t)(Hq + g) * hd + i);
+        }
+        const bf16* vsrc = row + (size_t)(Hq + Hkv) * hd;
+        const int vpv = hd >> 3;
+        for (int wi = threadIdx.x; wi < Hkv * vpv; wi += blockDim.x) {
+            const int g = wi / vpv, i = (wi - g * vpv) * 8;
+            *reinterpret_cast<uint4*>(vdst + (size_t)g * head_step + i) =
+                *reinterpret_cast<const uint4*>(vsrc + (size_t)g * hd + i);
+        }
+    }
+}
+
 RI_API int ri_rope_scatter(void* qkv, int act_dtype, int row_stride, const int* positions,
                            const float* cos_t, const float* sin_t, const int* slot_of_token,
                            void* cache, int tokens, int Hq, int Hkv, int hd, int rot,
@@ -174,6 +316,13 @@ RI_API int ri_rope_scatter(void* qkv, int act_dtype, int row_stride, const int* 
     cudaStream_t s = (cudaStream_t)stream;
     const int work = (Hq + 2 * Hkv) * hd / 2;
     const int threads = work >= 1024 ? 256 : 128;
+    if (act_dtype == RI_BF16 && hd % 16 == 0 && rot % 16 == 0 && row_stride % 8 == 0 && aligned16(qkv) &&
+        aligned16(cos_t) && aligned16(sin_t) && (!cache || aligned16(cache))) {
+        const int vt = work / 8 >= 256 ? 256 : (work / 8 >= 128 ? 128 : 64);
+        rope_scatter_bf16x8_kernel<<<tokens, vt, 0, s>>>((bf16*)qkv, row_stride, positions, cos_t, sin_t,
+                                                         slot_of_token, (bf16*)cache, Hq, Hkv, hd, rot, page_size);
+        return ri_launch_status();
+    }
     if (act_dtype == RI_BF16)
         rope_scatter_kernel<bf16><<<tokens, threads, 0, s>>>((bf16*)qkv, row_stride, positions, cos_t,
             sin_t, slot_of_token, (bf16*)cache, Hq, Hkv, hd, rot, page_size);
@@ -195,9 +344,33 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
     out[(size_t)t * inter + j] = from_f32<TA>(g / (1.0f + expf(-g)) * u);
 }
 
+// bf16, width a multiple of 8: 16 bytes of gate and of up per thread
+__global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int inter,
+                                       size_t n_vec) {
+    const int per_row = inter >> 3;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / per_row;
+        const int j = (int)(i - t * per_row) * 8;
+        const bf16* row = gu + t * 2 * (size_t)inter;
+        float g[8], u[8];
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(row + j), g);
+        bf16x8_to_float(*reinterpret_cast<const uint4*>(row + inter + j), u);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.0f + __expf(-g[k])) * u[k];
+        *reinterpret_cast<uint4*>(out + t * (size_t)inter + j) = float_to_bf16x8(g);
+    }
+}
+
 RI_API int ri_silu_mul(const void* gu, void* out, int act_dtype, int tokens, int inter, void* stream) {
     if (tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == RI_BF16 && inter % 8 == 0 && aligned16(gu) && aligned16(out)) {
+        const size_t n_vec = (size_t)tokens * (inter / 8);
+        size_t blocks = (n_vec + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        silu_mul_bf16x8_kernel<<<(int)blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, inter, n_vec);
+        return ri_launch_status();
+    }
     dim3 grid((inter + 255) / 256, tokens);
     if (act_dtype == RI_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)gu, (bf16*)out, inter);
     else silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gu, (float*)out, inter);
