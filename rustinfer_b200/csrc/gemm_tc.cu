@@ -1,0 +1,397 @@
+// C[M,N] = X[M,K] * W[N,K]^T in bf16 on the 5th-generation tensor cores: tcgen05.mma with
+// both operands staged in shared memory by TMA (128-byte swizzle) and the fp32 accumulator
+// in tensor memory, read back with tcgen05.ld for a fused epilogue.
+//
+// RustInfer sends these products to cuBLASLt, with a SIMT GEMV for one row
+// (crates/infer-backend-cuda/src/kernels/matmul/matmul.cu:131-650,870-934) and separate
+// kernels for SwiGLU and the residual add; it has no sm_100 path.  This kernel is the
+// engine's own: one CTA computes a 128 x BN tile (or a K-slice of it).
+//
+//   warp 0      TMA producer: one thread arms the stage's mbarrier and issues two loads
+//   warp 1      allocates tensor memory; one thread issues the MMAs and commits
+//   warps 2-5   epilogue: tcgen05.ld of their 32 lanes, then the fused store
+//
+// Orientation.  The 128-row operand of the MMA ("A") is the weight when few tokens are in
+// flight (decode: the weights stream through once, tokens are the narrow N of the MMA) and
+// the activations otherwise (prefill).  Split-K: grid.z CTAs take slices of K, park fp32
+// partial tiles in a workspace, and the CTA whose ticket is last adds them in slice order
+// (so the result does not depend on which CTA came last) and runs the epilogue.
+//
+// Epilogues: store bf16 / store fp32 / SiLU(gate)*up for a weight whose rows alternate
+// gate_j, up_j / add into the fp32 residual stream.
+//
+// Every wait on an mbarrier is bounded; on a time-out the kernel records a code in
+// *error, waits (bounded) for the copies it still has in flight, frees its tensor
+// memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+constexpr int BM = 128;                 // rows of the A operand per tile (MMA M)
+constexpr int BK = 64;                  // 64 bf16 = one 128-byte swizzle row
+constexpr int THREADS = 192;
+constexpr unsigned SPIN_LIMIT = 1u << 20;
+
+enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_RESIDUAL = 3 };
+enum ErrorCode { ERR_PRODUCER_WAIT = 1, ERR_MMA_WAIT = 2, ERR_EPILOGUE_WAIT = 3, ERR_DRAIN_WAIT = 4 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false after SPIN_LIMIT tries (about a tenth of a second), with `code` in *error.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* error, int code) {
+    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 1024) __nanosleep(64);
+    }
+    atomicExch(error, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// K-major tile of 128-byte rows, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(unsigned addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffff) >> 4);              // start address
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void mma_bf16_ss(unsigned tmem_d, uint64_t a, uint64_t b, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(unsigned addr, float (&v)[16]) {
+    unsigned r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN> struct Cfg {
+    static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
+    static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+struct Params {
+    int a_rows, b_rows;                  // valid rows of the A and B operands
+    int K;
+    int swap;                            // 1: A = weight (lanes = features), B = activations (columns = tokens)
+    int epilogue;
+    void* out;                           // bf16 or fp32 [tokens][ld_out]; fp32 residual stream for EPI_RESIDUAL
+    int ld_out;
+    int splits;
+    float* workspace;                    // [tiles][splits][BN][128] fp32
+    int* counters;                       // [tiles], zero between calls
+    int* error;
+    int tiles_a;
+};
+
+// one accumulator value of this thread: A-row `ra` (its TMEM lane), B-row `rb` (a column)
+__device__ __forceinline__ void store_one(const Params& p, int ra, int rb, float acc, float neighbour) {
+    const int feat = p.swap ? ra : rb, tok = p.swap ? rb : ra;
+    const int n_feat = p.swap ? p.a_rows : p.b_rows, n_tok = p.swap ? p.b_rows : p.a_rows;
+    if (feat >= n_feat || tok >= n_tok) return;
+    const size_t row = (size_t)tok * p.ld_out;
+    switch (p.epilogue) {
+        case EPI_BF16: reinterpret_cast<bf16*>(p.out)[row + feat] = __float2bfloat16_rn(acc); break;
+        case EPI_F32: reinterpret_cast<float*>(p.out)[row + feat] = acc; break;
+        case EPI_RESIDUAL: reinterpret_cast<float*>(p.out)[row + feat] += acc; break;
+        case EPI_SILU:                                   // even feature = gate_j, odd = up_j
+            if ((feat & 1) == 0)
+                reinterpret_cast<bf16*>(p.out)[row + (feat >> 1)] =
+                    __float2bfloat16_rn(acc / (1.0f + __expf(-acc)) * neighbour);
+            break;
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const Params p) {
+    using C = Cfg<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);      // swizzle atoms are 1 KiB
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_ready = empty + C::STAGES;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_ready + 1);
+    int* ticket_slot = reinterpret_cast<int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x;
+    const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+    const int a0 = ta * BM, b0 = tb * BN;
+    const int kblocks = (p.K + BK - 1) / BK;
+    const int per = (kblocks + p.splits - 1) / p.splits;
+    const int kb_begin = blockIdx.z * per;
+    const int kb_end = min(kb_begin + per, kblocks);
+    const int n_kb = max(kb_end - kb_begin, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % C::STAGES, round = i / C::STAGES;
+            if (round > 0) ok = mbar_wait(&empty[s], (round - 1) & 1, p.error, ERR_PRODUCER_WAIT);
+            if (!ok) break;
+            unsigned char* sa = tiles + (size_t)s * C::STAGE_BYTES;
+            mbar_expect_tx(&full[s], C::STAGE_BYTES);
+            tma_load_2d(sa, &map_a, &full[s], (kb_begin + i) * BK, a0);
+            tma_load_2d(sa + BM * BK * 2, &map_b, &full[s], (kb_begin + i) * BK, b0);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN, M = 128
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+        bool ok = true;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            const int s = i % C::STAGES, round = i / C::STAGES;
+            ok = mbar_wait(&full[s], round & 1, p.error, ERR_MMA_WAIT);
+            if (!ok) break;
+            tc_fence_after();
+            const unsigned sa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+            const unsigned sb = sa + BM * BK * 2;
+#pragma unroll
+            for (int k = 0; k < BK / 16; ++k)
+                mma_bf16_ss(tmem_base, smem_desc(sa + k * 32), smem_desc(sb + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+            tc_commit(&empty[s]);                         // the stage is free once these MMAs have read it
+        }
+        tc_commit(acc_ready);                             // the accumulator is complete
+        // every load that was issued has landed before shared memory is given up
+        for (int i = max(0, n_kb - C::STAGES); i < n_kb && !ok; ++i)
+            mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1, p.error, ERR_DRAIN_WAIT);
+    } else if (warp >= 2) {
+        // -------------------------------------------------------------------- epilogue
+        const int quarter = warp & 3;                     // the 32 TMEM lanes this warp may read
+        const int ra = a0 + quarter * 32 + lane;
+        bool ok = true;
+        if (n_kb > 0) ok = mbar_wait(acc_ready, 0, p.error, ERR_EPILOGUE_WAIT);
+        tc_fence_after();
+        const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
+        bool last = true;
+        if (p.splits > 1) {
+            // park this slice's partial tile, then find out whether we are the last slice
+            float* mine = p.workspace + ((size_t)tile * p.splits + blockIdx.z) * (BN * 128);
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (ok && n_kb > 0) tmem_ld16(taddr + c0, v);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * 128 + quarter * 32 + lane] = v[j];
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) *ticket_slot = atomicAdd(&p.counters[tile], 1);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            last = *ticket_slot == p.splits - 1;
+            if (last) {
+                __threadfence();
+                if (threadIdx.x == 64) p.counters[tile] = 0;
+            }
+        }
+        if (last) {
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (p.splits > 1) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    const float* base = p.workspace + (size_t)tile * p.splits * (BN * 128) + quarter * 32 + lane;
+                    for (int s = 0; s < p.splits; ++s)
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            v[j] += __ldcg(base + (size_t)s * (BN * 128) + (size_t)(c0 + j) * 128);
+                } else if (ok && n_kb > 0) {
+                    tmem_ld16(taddr + c0, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                }
+                if (p.epilogue == EPI_SILU && p.swap) {
+                    // lanes alternate gate, up: the even lane needs its odd neighbour's value
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                        store_one(p, ra, b0 + c0 + j, v[j], other);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        store_one(p, ra, b0 + c0 + j, v[j], (j & 1) ? 0.f : v[j + ((j & 1) ? 0 : 1)]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)C::TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host: tensor maps
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(sym);
+    }
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.ptr);
+        h ^= ((size_t)k.rows * 0x9E3779B97F4A7C15ull) ^ ((size_t)k.cols << 21) ^ ((size_t)k.box_rows << 43);
+        return h;
+    }
+};
+
+// A row-major bf16 matrix [rows][cols] seen as tiles of box_rows x 64 elements with the
+// 128-byte swizzle; rows and columns outside the matrix read as zero.
+int make_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    const MapKey key{ptr, rows, cols, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiled fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int BN>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int tiles, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)Cfg<BN>::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_tc_kernel<BN><<<dim3(tiles, 1, p.splits), THREADS, Cfg<BN>::SMEM, s>>>(ma, mb, p);
+    return ri_launch_status();
+}
+}  // namespace
+
+// Floats of workspace a call may need: tiles * splits * BN * 128 (0 when splits == 1).
+RI_API long long ri_gemm_tc_workspace_floats(int M, int N, int splits, int swap, int bn) {
+    if (splits <= 1) return 0;
+    const int a_rows = swap ? N : M, b_rows = swap ? M : N;
+    const long long tiles = (long long)((a_rows + BM - 1) / BM) * ((b_rows + bn - 1) / bn);
+    return tiles * splits * bn * 128;
+}
+
+// X [M][K] bf16 (row pitch K), W [N][K] bf16; out per `epilogue`:
+//   0 bf16 [M][ld_out], 1 fp32 [M][ld_out], 2 bf16 [M][ld_out] = silu(gate)*up with W's rows
+//   alternating gate_j, up_j (N = 2 * features of out), 3 fp32 [M][ld_out] += result.
+// swap: 1 puts the weight on the 128-row side of the MMA (few tokens), 0 the activations.
+// bn: rows of the other operand per tile (16, 32, 64, 128 or 256).  counters: one int per
+// tile, zero before the first call (the kernel leaves them zero).  error: one int that a
+// timed-out wait sets; zero it before use and read it when in doubt.
+RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* out, int ld_out, int epilogue,
+                      int swap, int bn, int splits, float* workspace, int* counters, int* error, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || splits < 1 || (splits > 1 && (!workspace || !counters)) || !error)
+        return (int)cudaErrorInvalidValue;
+    const void* A = swap ? W : X;
+    const void* B = swap ? X : W;
+    Params p;
+    p.a_rows = swap ? N : M;
+    p.b_rows = swap ? M : N;
+    p.K = K; p.swap = swap; p.epilogue = epilogue; p.out = out; p.ld_out = ld_out; p.splits = splits;
+    p.workspace = workspace; p.counters = counters; p.error = error;
+    p.tiles_a = (p.a_rows + BM - 1) / BM;
+    const int tiles_b = (p.b_rows + bn - 1) / bn;
+    CUtensorMap ma, mb;
+    int st = make_map(A, p.a_rows, K, BM, &ma);
+    if (st != 0) return st;
+    st = make_map(B, p.b_rows, K, bn, &mb);
+    if (st != 0) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int tiles = p.tiles_a * tiles_b;
+    switch (bn) {
+        case 16: return launch<16>(ma, mb, p, tiles, s);
+        case 32: return launch<32>(ma, mb, p, tiles, s);
+        case 64: return launch<64>(ma, mb, p, tiles, s);
+        case 128: return launch<128>(ma, mb, p, tiles, s);
+        case 256: return launch<256>(ma, mb, p, tiles, s);
+    }
+    return (int)cudaErrorInvalidValue;
+}

@@ -118,6 +118,86 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                                M, N, K, stream_ptr()), "gemm_f32")
 
 
+# ------------------------------------------------------------ tcgen05 bf16 matrix product
+EPI_BF16, EPI_F32, EPI_SILU, EPI_RESIDUAL = 0, 1, 2, 3
+_tc_state = {}
+_TC_WORKSPACE_FLOATS = 8 << 20
+_TC_COUNTERS = 1 << 14
+
+
+def gemm_tc_state(device: torch.device):
+    """(workspace fp32, tile counters int32, error flag int32) of the tensor-core GEMM on a
+    device; made once, so that captured graphs keep valid addresses."""
+    st = _tc_state.get(device)
+    if st is None:
+        st = (torch.empty(_TC_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
+              torch.zeros(_TC_COUNTERS, dtype=torch.int32, device=device),
+              torch.zeros(1, dtype=torch.int32, device=device))
+        _tc_state[device] = st
+    return st
+
+
+def gemm_tc_error(device: torch.device) -> int:
+    """The code a timed-out wait inside the tensor-core GEMM left (0: none); clears it."""
+    st = _tc_state.get(device)
+    if st is None:
+        return 0
+    code = int(st[2].item())
+    if code:
+        st[2].zero_()
+        st[1].zero_()
+    return code
+
+
+def gemm_tc_plan(M: int, N: int, K: int, num_sms: int = 148):
+    """(swap, bn, splits): which operand sits on the 128-row side of the MMA, the tile of
+    the other one, and how many K slices, so that about one wave of CTAs covers the GPU."""
+    if M <= 64:
+        swap, bn = 1, (16 if M <= 16 else 32 if M <= 32 else 64)
+        tiles = -(-N // 128)
+    else:
+        swap, bn = 0, (256 if N >= 256 else 128 if N > 64 else 64 if N > 32 else 32 if N > 16 else 16)
+        tiles = -(-M // 128) * -(-N // bn)
+    kblocks = -(-K // 64)
+    splits = 1
+    if tiles * 2 <= num_sms:
+        splits = max(1, min(num_sms // tiles, kblocks // 4, 32))
+        while splits > 1 and tiles * splits * bn * 128 > _TC_WORKSPACE_FLOATS:
+            splits -= 1
+    return swap, bn, splits
+
+
+def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.is_contiguous() and w.is_contiguous() and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16,
+            plan=None, num_sms: int = 148) -> None:
+    """out = x[M,K] @ w[N,K]^T on the tcgen05 tensor cores, bf16 inputs, fp32 accumulation.
+    epilogue: EPI_BF16 / EPI_F32 store into out [M,N]; EPI_SILU stores silu(gate)*up into
+    out [M,N/2] for a weight whose rows alternate gate_j, up_j; EPI_RESIDUAL adds into the
+    fp32 out [M,N]."""
+    require_cuda(x, w, out)
+    if not gemm_tc_supports(x, w):
+        raise KernelError("gemm_tc: contiguous, 16-byte aligned bfloat16 x [M,K] and w [N,K] with K a multiple of 8")
+    M, Kd = x.shape
+    N = w.shape[0]
+    if w.shape[1] != Kd or out.stride(1) != 1:
+        raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    cols = N // 2 if epilogue == EPI_SILU else N
+    want = torch.bfloat16 if epilogue in (EPI_BF16, EPI_SILU) else torch.float32
+    if out.dtype != want or out.shape != (M, cols) or (epilogue == EPI_SILU and N % 2):
+        raise KernelError(f"gemm_tc: out must be {want} [{M}, {cols}] for epilogue {epilogue}")
+    swap, bn, splits = plan or gemm_tc_plan(M, N, Kd, num_sms)
+    ws, counters, err = gemm_tc_state(x.device)
+    tiles = (-(-N // 128)) * (-(-M // bn)) if swap else (-(-M // 128)) * (-(-N // bn))
+    if tiles > counters.numel() or (splits > 1 and tiles * splits * bn * 128 > ws.numel()):
+        raise KernelError("gemm_tc: the split-K workspace is too small for this plan")
+    check(L.gemm_tc().ri_gemm_tc(_p(x), _p(w), M, N, Kd, _p(out), out.stride(0), epilogue, swap, bn, splits,
+                                 _p(ws), _p(counters), _p(err), stream_ptr()), "gemm_tc")
+
+
 def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                     cu_q: torch.Tensor, kv_len: torch.Tensor, tile_entry: torch.Tensor,
                     tile_q0: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,

@@ -29,6 +29,7 @@ _SIGNATURES = {
     "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
     "ri_attention_mma_tokens_per_tile": [_I],
+    "ri_gemm_tc": [_P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
 }
 
@@ -69,6 +70,10 @@ def attention_plain(head_dim: int) -> ctypes.CDLL:
     return _load(f"ri_attention_plain_hd{head_dim}", ["attention_plain.cu"], [f"RI_HEAD_DIM={head_dim}"])
 
 
+def gemm_tc() -> ctypes.CDLL:
+    return _load("ri_gemm_tc", ["gemm_tc.cu"])
+
+
 MMA_MAX_HEAD_DIM = 256
 
 
@@ -82,6 +87,7 @@ def attention_mma(head_dim: int) -> ctypes.CDLL:
 def build_all(head_dims) -> None:
     """Compile every library for the given head sizes (the ahead-of-time build check)."""
     core()
+    gemm_tc()
     for hd in head_dims:
         attention_plain(hd)
         if hd <= MMA_MAX_HEAD_DIM:
