@@ -95,6 +95,8 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                const int* __restrict__ tile_entry, const int* __restrict__ tile_tok0,
                int Hq, int Hkv, int Gc, int chunks, int tpt, int page_size, float scale_log2, int window) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);            // [MT][ROW]
     bf16* KVs = Qs + MT * ROW;                               // [2 buffers][K|V][KT][ROW]
@@ -262,6 +264,8 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
               const int* __restrict__ entry_list, int Hq, int Hkv, int Gc, int chunks, int page_size,
               float scale_log2, int window, int splits, float* __restrict__ part_o,
               float* __restrict__ part_lse) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);            // [16][ROW]
     bf16* KVs = Qs + 16 * ROW;                               // [2][K|V][KT][ROW]
@@ -428,6 +432,8 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
 __global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                bf16* __restrict__ out, int out_stride, const int* __restrict__ cu_q,
                                const int* __restrict__ entry_list, int Hq, int splits) {
+    pdl_trigger();
+    pdl_wait();
     const int slot = blockIdx.x, head = blockIdx.y;
     const int b = entry_list ? entry_list[slot] : slot;
     if (b < 0) return;
@@ -487,10 +493,10 @@ RI_API int ri_attention_prefill_bf16(const void* q, int q_stride, void* out, int
     if (st != 0) return st;
     const int G = Hq / Hkv, Gc = G < MT ? G : MT, chunks = (G + Gc - 1) / Gc, tpt = MT / Gc;
     dim3 grid(n_tiles, Hkv * chunks);
-    prefill_kernel<<<grid, THREADS, PREFILL_SMEM, (cudaStream_t)stream>>>(
+    RI_CHECKED(ri_launch(prefill_kernel, dim3(grid), dim3(THREADS), PREFILL_SMEM, (cudaStream_t)stream, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
         cu_q, kv_len, tile_entry, tile_tok0, Hq, Hkv, Gc, chunks, tpt, page_size,
-        scale * 1.4426950408889634f, window);
+        scale * 1.4426950408889634f, window));
     return ri_launch_status();
 }
 
@@ -508,14 +514,14 @@ RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int 
     const int G = Hq / Hkv, Gc = G < 16 ? G : 16, chunks = (G + Gc - 1) / Gc;
     dim3 grid(Hkv * chunks, splits, n_entries);
     cudaStream_t s = (cudaStream_t)stream;
-    decode_kernel<<<grid, THREADS, DECODE_SMEM, s>>>(
+    RI_CHECKED(ri_launch(decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, s, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
         cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,
-        splits, part_o, part_lse);
+        splits, part_o, part_lse));
     st = ri_launch_status();
     if (st != 0 || splits == 1) return st;
-    combine_kernel<<<dim3(n_entries, Hq), HD < 128 ? 64 : 128, 0, s>>>(
-        part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits);
+    RI_CHECKED(ri_launch(combine_kernel, dim3(dim3(n_entries, Hq)), dim3(HD < 128 ? 64 : 128), 0, s, 
+        part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits));
     return ri_launch_status();
 }
 
@@ -592,13 +598,15 @@ int ri_attention_decode_bf16_static(const void* q, int q_stride, void* out, int 
     const int G = Hq / Hkv, Gc = G < 16 ? G : 16, chunks = (G + Gc - 1) / Gc;
     dim3 grid(Hkv * chunks, splits, n_entries);
     cudaStream_t s = (cudaStream_t)stream;
-    decode_kernel<<<grid, THREADS, DECODE_SMEM, s>>>(
+    RI_CHECKED(ri_launch(decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, s, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
         cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,
-        splits, part_o, part_lse);
+        splits, part_o, part_lse));
     st = ri_launch_status();
     if (st != 0 || splits == 1) return st;
-    combine_kernel<<<dim3(n_entries, Hq), HD < 128 ? 64 : 128, 0, s>>>(
-        part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits);
+    RI_CHECKED(ri_launch(combine_kernel, dim3(dim3(n_entries, Hq)), dim3(HD < 128 ? 64 : 128), 0, s, 
+        part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits));
     return ri_launch_status();
 }
+
+RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }

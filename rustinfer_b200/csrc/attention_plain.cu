@@ -37,6 +37,8 @@ attention_plain_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        int table_stride, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                        const int* __restrict__ tile_entry, const int* __restrict__ tile_q0,
                        int Hq, int Hkv, int page_size, float scale, int window) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     float* Qs = smem;
     float* Ks = Qs + QT * QS;
@@ -160,9 +162,9 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* c
         configured = true;
     }
     dim3 grid(n_tiles, Hq);
-    attention_plain_kernel<T><<<grid, THREADS, smem, s>>>(
+    RI_CHECKED(ri_launch(attention_plain_kernel<T>, dim3(grid), dim3(THREADS), smem, s, 
         (const T*)q, q_stride, (T*)out, out_stride, (const T*)cache, block_table, table_stride,
-        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window);
+        cu_q, kv_len, tile_entry, tile_q0, Hq, Hkv, page_size, scale, window));
     return ri_launch_status();
 }
 }  // namespace
@@ -187,3 +189,5 @@ RI_API int ri_attention_plain(const void* q, int q_stride, void* out, int out_st
     return launch<float>(q, q_stride, out, out_stride, cache, block_table, table_stride, cu_q,
                          kv_len, tile_entry, tile_q0, n_tiles, Hq, Hkv, page_size, scale, window, s);
 }
+
+RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }

@@ -53,4 +53,37 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats *
 
 static inline int ri_launch_status() { return (int)cudaGetLastError(); }
 
+// ---- programmatic dependent launch -------------------------------------------------
+// Kernels of one step run back to back on one stream.  Launched with the programmatic-
+// serialization attribute, a kernel may begin (set up barriers, fetch weights that no
+// earlier kernel writes) while its predecessor is still draining; it calls pdl_wait()
+// before it touches anything the predecessor produced.  Every kernel launched this way
+// calls pdl_wait(), so completion is transitive along the chain.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#define RI_CHECKED(expr) do { int ri_st_ = (expr); if (ri_st_ != 0) return ri_st_; } while (0)
+
+// 1 (default): launch with the attribute; 0: plain launches.  One flag per library.
+inline int& ri_pdl_flag() {
+    static int on = 1;
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int ri_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                            Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ri_pdl_flag() ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 RI_API const char* ri_error_string(int code);

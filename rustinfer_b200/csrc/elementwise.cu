@@ -18,6 +18,8 @@ RI_API const char* ri_error_string(int code) { return cudaGetErrorString((cudaEr
 template <typename TW>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const TW* __restrict__ table,
                                     float* __restrict__ out, int d, int vocab) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * d;
@@ -35,9 +37,9 @@ RI_API int ri_embed_gather(const int* ids, const void* table, int table_dtype, f
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == RI_BF16)
-        embed_gather_kernel<bf16><<<tokens, threads, 0, s>>>(ids, (const bf16*)table, out, d, vocab);
+        RI_CHECKED(ri_launch(embed_gather_kernel<bf16>, dim3(tokens), dim3(threads), 0, s, ids, (const bf16*)table, out, d, vocab));
     else
-        embed_gather_kernel<float><<<tokens, threads, 0, s>>>(ids, (const float*)table, out, d, vocab);
+        RI_CHECKED(ri_launch(embed_gather_kernel<float>, dim3(tokens), dim3(threads), 0, s, ids, (const float*)table, out, d, vocab));
     return ri_launch_status();
 }
 
@@ -49,6 +51,8 @@ template <typename TA, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__ delta,
                                    const TW* __restrict__ w, float eps, TA* __restrict__ out,
                                    const int* __restrict__ rows, int d) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -96,6 +100,8 @@ template <typename TW>
 __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ h, const bf16* __restrict__ delta,
                                           const TW* __restrict__ w, float eps, bf16* __restrict__ out,
                                           const int* __restrict__ rows, int d) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float red[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -150,17 +156,17 @@ RI_API int ri_add_rmsnorm(float* h, const void* delta, const void* w, int w_dtyp
         (!delta || aligned16(delta))) {
         const int vt = ((d / 8 + 31) / 32) * 32;
         if (w_dtype == RI_BF16)
-            add_rmsnorm_bf16x8_kernel<bf16><<<n_rows, vt, 0, s>>>(h, (const bf16*)delta, (const bf16*)w, eps,
-                                                                  (bf16*)out, rows, d);
+            RI_CHECKED(ri_launch(add_rmsnorm_bf16x8_kernel<bf16>, dim3(n_rows), dim3(vt), 0, s, h, (const bf16*)delta, (const bf16*)w, eps,
+                                                                  (bf16*)out, rows, d));
         else
-            add_rmsnorm_bf16x8_kernel<float><<<n_rows, vt, 0, s>>>(h, (const bf16*)delta, (const float*)w, eps,
-                                                                   (bf16*)out, rows, d);
+            RI_CHECKED(ri_launch(add_rmsnorm_bf16x8_kernel<float>, dim3(n_rows), dim3(vt), 0, s, h, (const bf16*)delta, (const float*)w, eps,
+                                                                   (bf16*)out, rows, d));
         return ri_launch_status();
     }
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
 #define RI_LAUNCH(TA, TW)                                                                  \
-    add_rmsnorm_kernel<TA, TW><<<n_rows, threads, 0, s>>>(h, (const TA*)delta, (const TW*)w, \
-                                                          eps, (TA*)out, rows, d)
+    RI_CHECKED(ri_launch(add_rmsnorm_kernel<TA, TW>, dim3(n_rows), dim3(threads), 0, s, h, (const TA*)delta, (const TW*)w, \
+                                                          eps, (TA*)out, rows, d))
     if (act_dtype == RI_BF16) {
         if (w_dtype == RI_BF16) RI_LAUNCH(bf16, bf16); else RI_LAUNCH(bf16, float);
     } else {
@@ -173,6 +179,8 @@ RI_API int ri_add_rmsnorm(float* h, const void* delta, const void* w, int w_dtyp
 // h += delta on every row (flush of the last pending residual when the stream itself is wanted)
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ h, const TA* __restrict__ delta, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < n; i += stride) h[i] += to_f32<TA>(delta[i]);
@@ -183,8 +191,8 @@ RI_API int ri_residual_add(float* h, const void* delta, int act_dtype, long long
     cudaStream_t s = (cudaStream_t)stream;
     int blocks = (int)((n + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
-    if (act_dtype == RI_BF16) residual_add_kernel<bf16><<<blocks, 256, 0, s>>>(h, (const bf16*)delta, (size_t)n);
-    else residual_add_kernel<float><<<blocks, 256, 0, s>>>(h, (const float*)delta, (size_t)n);
+    if (act_dtype == RI_BF16) RI_CHECKED(ri_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, s, h, (const bf16*)delta, (size_t)n));
+    else RI_CHECKED(ri_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, s, h, (const float*)delta, (size_t)n));
     return ri_launch_status();
 }
 
@@ -200,6 +208,8 @@ __global__ void rope_scatter_kernel(TA* __restrict__ qkv, int row_stride,
                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                     const int* __restrict__ slot_of_token, TA* __restrict__ cache,
                                     int Hq, int Hkv, int hd, int rot, int page_size) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int pos = positions[t];
@@ -253,6 +263,8 @@ __global__ void rope_scatter_bf16x8_kernel(bf16* __restrict__ qkv, int row_strid
                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                            const int* __restrict__ slot_of_token, bf16* __restrict__ cache,
                                            int Hq, int Hkv, int hd, int rot, int page_size) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int pos = positions[t];
@@ -319,16 +331,16 @@ RI_API int ri_rope_scatter(void* qkv, int act_dtype, int row_stride, const int* 
     if (act_dtype == RI_BF16 && hd % 16 == 0 && rot % 16 == 0 && row_stride % 8 == 0 && aligned16(qkv) &&
         aligned16(cos_t) && aligned16(sin_t) && (!cache || aligned16(cache))) {
         const int vt = work / 8 >= 256 ? 256 : (work / 8 >= 128 ? 128 : 64);
-        rope_scatter_bf16x8_kernel<<<tokens, vt, 0, s>>>((bf16*)qkv, row_stride, positions, cos_t, sin_t,
-                                                         slot_of_token, (bf16*)cache, Hq, Hkv, hd, rot, page_size);
+        RI_CHECKED(ri_launch(rope_scatter_bf16x8_kernel, dim3(tokens), dim3(vt), 0, s, (bf16*)qkv, row_stride, positions, cos_t, sin_t,
+                                                         slot_of_token, (bf16*)cache, Hq, Hkv, hd, rot, page_size));
         return ri_launch_status();
     }
     if (act_dtype == RI_BF16)
-        rope_scatter_kernel<bf16><<<tokens, threads, 0, s>>>((bf16*)qkv, row_stride, positions, cos_t,
-            sin_t, slot_of_token, (bf16*)cache, Hq, Hkv, hd, rot, page_size);
+        RI_CHECKED(ri_launch(rope_scatter_kernel<bf16>, dim3(tokens), dim3(threads), 0, s, (bf16*)qkv, row_stride, positions, cos_t,
+            sin_t, slot_of_token, (bf16*)cache, Hq, Hkv, hd, rot, page_size));
     else
-        rope_scatter_kernel<float><<<tokens, threads, 0, s>>>((float*)qkv, row_stride, positions, cos_t,
-            sin_t, slot_of_token, (float*)cache, Hq, Hkv, hd, rot, page_size);
+        RI_CHECKED(ri_launch(rope_scatter_kernel<float>, dim3(tokens), dim3(threads), 0, s, (float*)qkv, row_stride, positions, cos_t,
+            sin_t, slot_of_token, (float*)cache, Hq, Hkv, hd, rot, page_size));
     return ri_launch_status();
 }
 
@@ -336,6 +348,8 @@ RI_API int ri_rope_scatter(void* qkv, int act_dtype, int row_stride, const int* 
 // gu row: [gate (I) | up (I)]; out[t, j] = gate / (1 + e^-gate) * up.
 template <typename TA>
 __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.y;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= inter) return;
@@ -347,6 +361,8 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
 // bf16, width a multiple of 8: 16 bytes of gate and of up per thread
 __global__ void silu_mul_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int inter,
                                        size_t n_vec) {
+    pdl_trigger();
+    pdl_wait();
     const int per_row = inter >> 3;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / per_row;
@@ -368,11 +384,13 @@ RI_API int ri_silu_mul(const void* gu, void* out, int act_dtype, int tokens, int
         const size_t n_vec = (size_t)tokens * (inter / 8);
         size_t blocks = (n_vec + 255) / 256;
         if (blocks > 148 * 16) blocks = 148 * 16;
-        silu_mul_bf16x8_kernel<<<(int)blocks, 256, 0, s>>>((const bf16*)gu, (bf16*)out, inter, n_vec);
+        RI_CHECKED(ri_launch(silu_mul_bf16x8_kernel, dim3((int)blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, inter, n_vec));
         return ri_launch_status();
     }
     dim3 grid((inter + 255) / 256, tokens);
-    if (act_dtype == RI_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)gu, (bf16*)out, inter);
-    else silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gu, (float*)out, inter);
+    if (act_dtype == RI_BF16) RI_CHECKED(ri_launch(silu_mul_kernel<bf16>, dim3(grid), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, inter));
+    else RI_CHECKED(ri_launch(silu_mul_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)gu, (float*)out, inter));
     return ri_launch_status();
 }
+
+RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }

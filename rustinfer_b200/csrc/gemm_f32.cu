@@ -14,6 +14,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw,
                 float* __restrict__ C, int ldc, int M, int N, int K) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -67,6 +69,6 @@ RI_API int ri_gemm_f32(const float* A, int lda, const float* W, int ldw, float* 
                        int M, int N, int K, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, lda, W, ldw, C, ldc, M, N, K);
+    RI_CHECKED(ri_launch(gemm_f32_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, A, lda, W, ldw, C, ldc, M, N, K));
     return ri_launch_status();
 }

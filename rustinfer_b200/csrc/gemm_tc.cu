@@ -103,7 +103,8 @@ template <int BN> struct Cfg {
     static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
     static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int ACC_COLS = BN < 32 ? 32 : BN;      // columns of one accumulator
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;          // two accumulators: epilogue and MMA overlap
     static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
@@ -114,17 +115,20 @@ struct Params {
     int epilogue;
     void* out;                           // bf16 or fp32 [tokens][ld_out]; fp32 residual stream for EPI_RESIDUAL
     int ld_out;
+    int vec;                             // rows of out start on 16-byte boundaries: vector stores allowed
     int splits;
     float* workspace;                    // [tiles][splits][BN][128] fp32
     int* counters;                       // [tiles], zero between calls
     int* error;
-    int tiles_a;
+    int tiles_a, n_tiles;
+    int a_box;                           // rows of A per tile actually loaded (<= 128, a multiple of 8)
 };
 
-// one accumulator value of this thread: A-row `ra` (its TMEM lane), B-row `rb` (a column)
-__device__ __forceinline__ void store_one(const Params& p, int ra, int rb, float acc, float neighbour) {
-    const int feat = p.swap ? ra : rb, tok = p.swap ? rb : ra;
-    const int n_feat = p.swap ? p.a_rows : p.b_rows, n_tok = p.swap ? p.b_rows : p.a_rows;
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+// one accumulator value: token `tok`, feature `feat` (neighbour: the value of feature feat + 1)
+__device__ __forceinline__ void store_one(const Params& p, int n_tok, int n_feat, int tok, int feat,
+                                          float acc, float neighbour) {
     if (feat >= n_feat || tok >= n_tok) return;
     const size_t row = (size_t)tok * p.ld_out;
     switch (p.epilogue) {
@@ -133,12 +137,66 @@ __device__ __forceinline__ void store_one(const Params& p, int ra, int rb, float
         case EPI_RESIDUAL: reinterpret_cast<float*>(p.out)[row + feat] += acc; break;
         case EPI_SILU:                                   // even feature = gate_j, odd = up_j
             if ((feat & 1) == 0)
-                reinterpret_cast<bf16*>(p.out)[row + (feat >> 1)] =
-                    __float2bfloat16_rn(acc / (1.0f + __expf(-acc)) * neighbour);
+                reinterpret_cast<bf16*>(p.out)[row + (feat >> 1)] = __float2bfloat16_rn(silu_mul(acc, neighbour));
             break;
     }
 }
 
+__device__ __forceinline__ uint4 pack8(const float* v) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    return r;
+}
+
+// 16 consecutive features of one token (activations on the 128-row side)
+__device__ __forceinline__ void store_row16(const Params& p, int tok, int feat0, const float (&v)[16]) {
+    if (tok >= p.a_rows) return;
+    if (!p.vec || feat0 + 16 > p.b_rows) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) store_one(p, p.a_rows, p.b_rows, tok, feat0 + j, v[j], j < 15 ? v[j + 1] : 0.f);
+        return;
+    }
+    const size_t row = (size_t)tok * p.ld_out;
+    switch (p.epilogue) {
+        case EPI_BF16: {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
+            dst[0] = pack8(v);
+            dst[1] = pack8(v + 8);
+            break;
+        }
+        case EPI_F32: {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + row + feat0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            break;
+        }
+        case EPI_RESIDUAL: {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + row + feat0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float4 h = dst[j];
+                h.x += v[4 * j]; h.y += v[4 * j + 1]; h.z += v[4 * j + 2]; h.w += v[4 * j + 3];
+                dst[j] = h;
+            }
+            break;
+        }
+        case EPI_SILU: {
+            float m[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m[j] = silu_mul(v[2 * j], v[2 * j + 1]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + (feat0 >> 1)) = pack8(m);
+            break;
+        }
+    }
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent over tiles: CTA x takes tiles x, x + gridDim.x, ...; blockIdx.z is the K slice.
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -149,14 +207,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);      // swizzle atoms are 1 KiB
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
     uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_ready = empty + C::STAGES;
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_ready + 1);
+    uint64_t* acc_full = empty + C::STAGES;              // [2] accumulator written, epilogue may read
+    uint64_t* acc_empty = acc_full + 2;                  // [2] accumulator read, MMA may overwrite
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
     int* ticket_slot = reinterpret_cast<int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x;
-    const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
-    const int a0 = ta * BM, b0 = tb * BN;
     const int kblocks = (p.K + BK - 1) / BK;
     const int per = (kblocks + p.splits - 1) / p.splits;
     const int kb_begin = blockIdx.z * per;
@@ -165,7 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -180,99 +236,163 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
+        // The weight tiles of the first stages are fetched before the dependency wait: no
+        // earlier kernel writes weights, so they stream in while the predecessor drains.
+        const CUtensorMap* wmap = p.swap ? &map_a : &map_b;
+        const CUtensorMap* xmap = p.swap ? &map_b : &map_a;
+        const int woff = p.swap ? 0 : BM * BK * 2, xoff = p.swap ? BM * BK * 2 : 0;
+        const unsigned stage_tx = (unsigned)(p.a_box + BN) * BK * 2;   // bytes the two boxes of a stage bring
+        pdl_trigger();
+        const int pre = blockIdx.x < p.n_tiles ? min(n_kb, C::STAGES) : 0;
+        {
+            const int tile = blockIdx.x;
+            const int w0 = p.swap ? (tile % p.tiles_a) * p.a_box : (tile / p.tiles_a) * BN;
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(&full[i], stage_tx);
+                tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + woff, wmap, &full[i], (kb_begin + i) * BK, w0);
+            }
+        }
+        pdl_wait();
         bool ok = true;
-        for (int i = 0; i < n_kb && ok; ++i) {
-            const int s = i % C::STAGES, round = i / C::STAGES;
-            if (round > 0) ok = mbar_wait(&empty[s], (round - 1) & 1, p.error, ERR_PRODUCER_WAIT);
-            if (!ok) break;
-            unsigned char* sa = tiles + (size_t)s * C::STAGE_BYTES;
-            mbar_expect_tx(&full[s], C::STAGE_BYTES);
-            tma_load_2d(sa, &map_a, &full[s], (kb_begin + i) * BK, a0);
-            tma_load_2d(sa + BM * BK * 2, &map_b, &full[s], (kb_begin + i) * BK, b0);
+        int it = 0;                                       // k-blocks loaded so far, over all tiles
+        for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
+            const int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
+            const int w0 = p.swap ? a0 : b0, x0 = p.swap ? b0 : a0;
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % C::STAGES, round = it / C::STAGES;
+                unsigned char* st = tiles + (size_t)s * C::STAGE_BYTES;
+                if (it >= pre) {
+                    if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, p.error, ERR_PRODUCER_WAIT)) { ok = false; break; }
+                    mbar_expect_tx(&full[s], stage_tx);
+                    tma_load_2d(st + woff, wmap, &full[s], (kb_begin + i) * BK, w0);
+                }
+                tma_load_2d(st + xoff, xmap, &full[s], (kb_begin + i) * BK, x0);
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN, M = 128
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
         bool ok = true;
-        for (int i = 0; i < n_kb && ok; ++i) {
-            const int s = i % C::STAGES, round = i / C::STAGES;
-            ok = mbar_wait(&full[s], round & 1, p.error, ERR_MMA_WAIT);
-            if (!ok) break;
+        int it = 0, t = 0;
+        for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x, ++t) {
+            const int buf = t & 1, use = t >> 1;
+            // the epilogue has emptied this accumulator (first use of a buffer passes at once)
+            if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
             tc_fence_after();
-            const unsigned sa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
-            const unsigned sb = sa + BM * BK * 2;
+            const unsigned tmem_d = tmem_base + buf * C::ACC_COLS;
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                const int s = it % C::STAGES, round = it / C::STAGES;
+                if (!mbar_wait(&full[s], round & 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
+                tc_fence_after();
+                const unsigned sa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
+                const unsigned sb = sa + BM * BK * 2;
 #pragma unroll
-            for (int k = 0; k < BK / 16; ++k)
-                mma_bf16_ss(tmem_base, smem_desc(sa + k * 32), smem_desc(sb + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
-            tc_commit(&empty[s]);                         // the stage is free once these MMAs have read it
+                for (int k = 0; k < BK / 16; ++k)
+                    mma_bf16_ss(tmem_d, smem_desc(sa + k * 32), smem_desc(sb + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                tc_commit(&empty[s]);                     // the stage is free once these MMAs have read it
+            }
+            tc_commit(&acc_full[buf]);                    // the accumulator is complete
         }
-        tc_commit(acc_ready);                             // the accumulator is complete
-        // every load that was issued has landed before shared memory is given up
-        for (int i = max(0, n_kb - C::STAGES); i < n_kb && !ok; ++i)
-            mbar_wait(&full[i % C::STAGES], (i / C::STAGES) & 1, p.error, ERR_DRAIN_WAIT);
+        if (!ok) {
+            // whatever was loaded last must have landed before shared memory is given up
+            for (int s = 0; s < C::STAGES; ++s)
+                for (int par = 0; par < 2; ++par)
+                    if (mbar_try_wait(&full[s], par)) break;
+            for (unsigned spin = 0; spin < 4096; ++spin) __nanosleep(256);
+        }
     } else if (warp >= 2) {
         // -------------------------------------------------------------------- epilogue
         const int quarter = warp & 3;                     // the 32 TMEM lanes this warp may read
-        const int ra = a0 + quarter * 32 + lane;
         bool ok = true;
-        if (n_kb > 0) ok = mbar_wait(acc_ready, 0, p.error, ERR_EPILOGUE_WAIT);
-        tc_fence_after();
-        const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
-        bool last = true;
-        if (p.splits > 1) {
-            // park this slice's partial tile, then find out whether we are the last slice
-            float* mine = p.workspace + ((size_t)tile * p.splits + blockIdx.z) * (BN * 128);
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                if (ok && n_kb > 0) tmem_ld16(taddr + c0, v);
-                else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * 128 + quarter * 32 + lane] = v[j];
-            }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 64) *ticket_slot = atomicAdd(&p.counters[tile], 1);
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            last = *ticket_slot == p.splits - 1;
-            if (last) {
-                __threadfence();
-                if (threadIdx.x == 64) p.counters[tile] = 0;
-            }
-        }
-        if (last) {
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                float v[16];
-                if (p.splits > 1) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                    const float* base = p.workspace + (size_t)tile * p.splits * (BN * 128) + quarter * 32 + lane;
-                    for (int s = 0; s < p.splits; ++s)
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            v[j] += __ldcg(base + (size_t)s * (BN * 128) + (size_t)(c0 + j) * 128);
-                } else if (ok && n_kb > 0) {
+        int t = 0;
+        pdl_wait();                                       // out, workspace and counters belong to earlier kernels till now
+        const bool atomic_out = p.splits > 1 && p.epilogue == EPI_RESIDUAL;
+        for (int tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x, ++t) {
+            const int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
+            // lanes beyond the rows this tile loaded hold nothing of this tile
+            const int ra = quarter * 32 + lane < p.a_box ? a0 + quarter * 32 + lane : 0x3fffffff;
+            const int buf = t & 1, use = t >> 1;
+            if (ok && n_kb > 0) ok = mbar_wait(&acc_full[buf], use & 1, p.error, ERR_EPILOGUE_WAIT);
+            tc_fence_after();
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + buf * C::ACC_COLS;
+            const bool have = ok && n_kb > 0;
+            bool last = true;
+            if (atomic_out) {
+                // K slices of a product that is added into the fp32 stream: every slice adds
+                // its own part, no meeting point needed (the order of the adds is not fixed)
+                last = false;
+                float* h = reinterpret_cast<float*>(p.out);
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    if (!have) break;
                     tmem_ld16(taddr + c0, v);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = 0.f;
-                }
-                if (p.epilogue == EPI_SILU && p.swap) {
-                    // lanes alternate gate, up: the even lane needs its odd neighbour's value
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
-                        store_one(p, ra, b0 + c0 + j, v[j], other);
+                        const int tok = p.swap ? b0 + c0 + j : ra, feat = p.swap ? ra : b0 + c0 + j;
+                        const int n_tok = p.swap ? p.b_rows : p.a_rows, n_feat = p.swap ? p.a_rows : p.b_rows;
+                        if (tok < n_tok && feat < n_feat) atomicAdd(h + (size_t)tok * p.ld_out + feat, v[j]);
                     }
-                } else {
+                }
+            } else if (p.splits > 1) {
+                // park this slice's partial tile, then find out whether we are the last slice
+                float* mine = p.workspace + ((size_t)tile * p.splits + blockIdx.z) * (BN * 128);
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    if (have) tmem_ld16(taddr + c0, v);
+                    else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        store_one(p, ra, b0 + c0 + j, v[j], (j & 1) ? 0.f : v[j + ((j & 1) ? 0 : 1)]);
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * 128 + quarter * 32 + lane] = v[j];
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) *ticket_slot = atomicAdd(&p.counters[tile], 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                last = *ticket_slot == p.splits - 1;
+                if (last) {
+                    __threadfence();
+                    if (threadIdx.x == 64) p.counters[tile] = 0;
                 }
             }
+            if (last) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    if (p.splits > 1) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                        const float* base = p.workspace + (size_t)tile * p.splits * (BN * 128) + quarter * 32 + lane;
+                        for (int s = 0; s < p.splits; ++s)
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                v[j] += __ldcg(base + (size_t)s * (BN * 128) + (size_t)(c0 + j) * 128);
+                    } else if (have) {
+                        tmem_ld16(taddr + c0, v);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = 0.f;
+                    }
+                    if (!p.swap) {
+                        store_row16(p, ra, b0 + c0, v);
+                    } else if (p.epilogue == EPI_SILU) {
+                        // lanes alternate gate, up: the even lane needs its odd neighbour's value
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                            store_one(p, p.b_rows, p.a_rows, b0 + c0 + j, ra, v[j], other);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) store_one(p, p.b_rows, p.a_rows, b0 + c0 + j, ra, v[j], 0.f);
+                    }
+                }
+            }
+            // this accumulator may be overwritten by the tile after next
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
@@ -345,7 +465,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int ti
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tc_kernel<BN><<<dim3(tiles, 1, p.splits), THREADS, Cfg<BN>::SMEM, s>>>(ma, mb, p);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    // one CTA per SM walks the tiles; with K slices every CTA has exactly one tile
+    const int ctas = (p.splits > 1 || tiles < sms) ? tiles : sms;
+    RI_CHECKED(ri_launch(gemm_tc_kernel<BN>, dim3(ctas, 1, p.splits), dim3(THREADS), Cfg<BN>::SMEM, s, ma, mb, p));
     return ri_launch_status();
 }
 }  // namespace
@@ -365,10 +493,16 @@ RI_API long long ri_gemm_tc_workspace_floats(int M, int N, int splits, int swap,
 // bn: rows of the other operand per tile (16, 32, 64, 128 or 256).  counters: one int per
 // tile, zero before the first call (the kernel leaves them zero).  error: one int that a
 // timed-out wait sets; zero it before use and read it when in doubt.
+RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }
+
+// a_box: rows of the 128-row operand a tile really covers (a multiple of 8 from 8 to 128;
+// fewer than 128 evens out the last wave of tiles over the SMs).
 RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* out, int ld_out, int epilogue,
-                      int swap, int bn, int splits, float* workspace, int* counters, int* error, void* stream) {
+                      int swap, int bn, int splits, int a_box, float* workspace, int* counters, int* error,
+                      void* stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || splits < 1 || (splits > 1 && (!workspace || !counters)) || !error)
+    if (K <= 0 || K % 8 != 0 || splits < 1 || (splits > 1 && (!workspace || !counters)) || !error ||
+        a_box < 8 || a_box > BM || a_box % 8 != 0)
         return (int)cudaErrorInvalidValue;
     const void* A = swap ? W : X;
     const void* B = swap ? X : W;
@@ -379,13 +513,19 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     p.workspace = workspace; p.counters = counters; p.error = error;
     p.tiles_a = (p.a_rows + BM - 1) / BM;
     const int tiles_b = (p.b_rows + bn - 1) / bn;
+    p.n_tiles = p.tiles_a * tiles_b;
+    const int esize = (epilogue == EPI_BF16 || epilogue == EPI_SILU) ? 2 : 4;
+    p.vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && ((size_t)ld_out * esize) % 16 == 0) ? 1 : 0;
     CUtensorMap ma, mb;
-    int st = make_map(A, p.a_rows, K, BM, &ma);
+    p.a_box = a_box;
+    p.tiles_a = (p.a_rows + a_box - 1) / a_box;
+    p.n_tiles = p.tiles_a * tiles_b;
+    int st = make_map(A, p.a_rows, K, a_box, &ma);
     if (st != 0) return st;
     st = make_map(B, p.b_rows, K, bn, &mb);
     if (st != 0) return st;
     cudaStream_t s = (cudaStream_t)stream;
-    const int tiles = p.tiles_a * tiles_b;
+    const int tiles = p.n_tiles;
     switch (bn) {
         case 16: return launch<16>(ma, mb, p, tiles, s);
         case 32: return launch<32>(ma, mb, p, tiles, s);

@@ -32,6 +32,8 @@ __device__ __forceinline__ float from_ordered(unsigned int k) {
 __global__ void __launch_bounds__(256)
 argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
               unsigned long long* __restrict__ state, unsigned int* __restrict__ count) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ unsigned long long best[8];
     const int row_id = blockIdx.y;
     const float* row = logits + (size_t)row_id * ld;
@@ -93,6 +95,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, int vpad,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ min_p, const double* __restrict__ draw,
               int* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ double buf[ST + 1];
     __shared__ int found;
     const int r = blockIdx.x, tid = threadIdx.x;
@@ -188,7 +192,7 @@ RI_API int ri_argmax(const float* logits, int ld, int rows, int vocab, int* out,
     const int cap = (4 * 148 + rows - 1) / rows;         // about four CTAs per SM in all
     if (per_row > cap) per_row = cap;
     if (per_row < 1) per_row = 1;
-    argmax_kernel<<<dim3(per_row, rows), 256, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out, state, count);
+    RI_CHECKED(ri_launch(argmax_kernel, dim3(dim3(per_row, rows)), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, out, state, count));
     return ri_launch_status();
 }
 
@@ -199,7 +203,7 @@ RI_API int ri_sample(const float* logits, int ld, int rows, int vocab, int vpad,
                      void* stream) {
     if (rows <= 0) return 0;
     if (vpad < vocab || (vpad & (vpad - 1)) != 0) return (int)cudaErrorInvalidValue;
-    sample_kernel<<<rows, ST, 0, (cudaStream_t)stream>>>(logits, ld, vocab, vpad, scratch, temperature,
-                                                         top_k, top_p, min_p, draw, out);
+    RI_CHECKED(ri_launch(sample_kernel, dim3(rows), dim3(ST), 0, (cudaStream_t)stream, logits, ld, vocab, vpad, scratch, temperature,
+                                                         top_k, top_p, min_p, draw, out));
     return ri_launch_status();
 }

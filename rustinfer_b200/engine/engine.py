@@ -158,4 +158,5 @@ class Engine:
             if not self.step() and not self.scheduler.has_work():
                 break
         self.stats.seconds += time.perf_counter() - t0
+        self.runner.check_kernel_errors()
         return [self.take_finished(i) for i in ids]

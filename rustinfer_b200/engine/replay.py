@@ -68,6 +68,7 @@ def main(argv: Optional[List[str]] = None) -> int:
                 os.replace(tmp, os.path.join(args.out, f"{step_no}.f32"))
             else:
                 torch.cuda.synchronize()
+            runner.check_kernel_errors()
         for rid in rec.get("end", []):
             if runner.cache.is_open(rid):
                 runner.close(rid)

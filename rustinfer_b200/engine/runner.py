@@ -476,6 +476,16 @@ class ModelRunner:
             return g.logits[: len(entries)]
         return g.logits[torch.tensor(wanted, device=self.device)]
 
+    def check_kernel_errors(self) -> None:
+        """Raise if a kernel recorded a fault it survived (a bounded wait that ran out).
+        Reads one word from the device, so it synchronises; callers use it where they
+        synchronise anyway."""
+        from ..ops import kernels as _k
+        code = _k.gemm_tc_error(self.device)
+        if code:
+            raise RuntimeError(f"the tensor-core matrix product gave up a wait (code {code}); "
+                               f"results of the last steps are not valid")
+
     def _zero_new_state(self) -> None:
         new = self.cache.newly_opened_slots
         if not new:

@@ -84,7 +84,7 @@ class Decoder:
         # the head is the embedding table when the file has no head of its own
         # (crates/infer-worker/src/models/decoder.rs:245-262)
         self.head_is_tied = head is None
-        self.head = Linear(self.embed_table if head is None else head)
+        self.head = Linear(self.embed_table if head is None else head, self.ctx.num_sms)
         self.final_norm.load({n: tensors[s.final_norm_name + n] for n in self.final_norm.param_decls()})
         for block, ls in zip(self.blocks, s.layers):
             for role, part in block.roles().items():

@@ -149,9 +149,10 @@ def gemm_tc_error(device: torch.device) -> int:
     return code
 
 
-def gemm_tc_plan(M: int, N: int, K: int, num_sms: int = 148):
-    """(swap, bn, splits): which operand sits on the 128-row side of the MMA, the tile of
-    the other one, and how many K slices, so that about one wave of CTAs covers the GPU."""
+def gemm_tc_plan(M: int, N: int, K: int, num_sms: int = 148, epilogue: int = EPI_BF16):
+    """(swap, bn, splits, a_box): which operand sits on the 128-row side of the MMA, the
+    tile of the other one, how many K slices, and how many rows of the 128 a tile really
+    covers, so that about one even wave of CTAs covers the GPU."""
     if M <= 64:
         swap, bn = 1, (16 if M <= 16 else 32 if M <= 32 else 64)
         tiles = -(-N // 128)
@@ -159,12 +160,17 @@ def gemm_tc_plan(M: int, N: int, K: int, num_sms: int = 148):
         swap, bn = 0, (256 if N >= 256 else 128 if N > 64 else 64 if N > 32 else 32 if N > 16 else 16)
         tiles = -(-M // 128) * -(-N // bn)
     kblocks = -(-K // 64)
-    splits = 1
+    splits, a_box = 1, 128
     if tiles * 2 <= num_sms:
         splits = max(1, min(num_sms // tiles, kblocks // 4, 32))
-        while splits > 1 and tiles * splits * bn * 128 > _TC_WORKSPACE_FLOATS:
-            splits -= 1
-    return swap, bn, splits
+        if epilogue != EPI_RESIDUAL:                       # slices meet in the workspace
+            while splits > 1 and tiles * splits * bn * 128 > _TC_WORKSPACE_FLOATS:
+                splits -= 1
+    elif swap:
+        # few tokens, no K slices: shrink the tiles until the last wave is as full as the others
+        waves = -(-tiles // num_sms)
+        a_box = min(128, max(64, 8 * -(-N // (8 * waves * num_sms))))
+    return swap, bn, splits, a_box
 
 
 def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -189,13 +195,16 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
     want = torch.bfloat16 if epilogue in (EPI_BF16, EPI_SILU) else torch.float32
     if out.dtype != want or out.shape != (M, cols) or (epilogue == EPI_SILU and N % 2):
         raise KernelError(f"gemm_tc: out must be {want} [{M}, {cols}] for epilogue {epilogue}")
-    swap, bn, splits = plan or gemm_tc_plan(M, N, Kd, num_sms)
+    plan = plan or gemm_tc_plan(M, N, Kd, num_sms, epilogue)
+    swap, bn, splits = plan[:3]
+    a_box = plan[3] if len(plan) > 3 else 128
     ws, counters, err = gemm_tc_state(x.device)
-    tiles = (-(-N // 128)) * (-(-M // bn)) if swap else (-(-M // 128)) * (-(-N // bn))
-    if tiles > counters.numel() or (splits > 1 and tiles * splits * bn * 128 > ws.numel()):
+    tiles = (-(-N // a_box)) * (-(-M // bn)) if swap else (-(-M // a_box)) * (-(-N // bn))
+    meets = splits > 1 and epilogue != EPI_RESIDUAL
+    if tiles > counters.numel() or (meets and tiles * splits * bn * 128 > ws.numel()):
         raise KernelError("gemm_tc: the split-K workspace is too small for this plan")
     check(L.gemm_tc().ri_gemm_tc(_p(x), _p(w), M, N, Kd, _p(out), out.stride(0), epilogue, swap, bn, splits,
-                                 _p(ws), _p(counters), _p(err), stream_ptr()), "gemm_tc")
+                                 a_box, _p(ws), _p(counters), _p(err), stream_ptr()), "gemm_tc")
 
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,

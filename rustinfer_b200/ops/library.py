@@ -6,6 +6,7 @@ There is no other implementation behind these wrappers: a missing library is an 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -29,7 +30,7 @@ _SIGNATURES = {
     "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
     "ri_attention_mma_tokens_per_tile": [_I],
-    "ri_gemm_tc": [_P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "ri_gemm_tc": [_P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
 }
 
@@ -50,11 +51,29 @@ def _bind(lib: ctypes.CDLL) -> ctypes.CDLL:
     return lib
 
 
+_pdl = os.environ.get("RUSTINFER_B200_PDL", "1") != "0"
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for every kernel of this package (default on; the
+    environment variable RUSTINFER_B200_PDL=0 turns it off): a kernel may start its set-up
+    while its predecessor on the stream drains."""
+    global _pdl
+    _pdl = bool(on)
+    for lib in _loaded.values():
+        if hasattr(lib, "ri_set_pdl"):
+            lib.ri_set_pdl(1 if _pdl else 0)
+
+
 def _load(name: str, sources, defines=()) -> ctypes.CDLL:
     lib = _loaded.get(name)
     if lib is None:
         path = build.build_library(name, sources, defines)
         lib = _bind(ctypes.CDLL(path))
+        if hasattr(lib, "ri_set_pdl"):
+            lib.ri_set_pdl.argtypes = [_I]
+            lib.ri_set_pdl.restype = None
+            lib.ri_set_pdl(1 if _pdl else 0)
         _loaded[name] = lib
     return lib
 

@@ -25,6 +25,7 @@ class GQAAttention(Mixer):
     keys or values and reads the cache another layer wrote)."""
 
     graph_safe = True
+    adds_to_residual = True
     MAX_SPLITS = 16
 
     def __init__(self, params):
@@ -90,10 +91,17 @@ class GQAAttention(Mixer):
         if self.own_kv:
             parts += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
         dt = torch.float32 if any(t.dtype == torch.float32 for t in parts) else parts[0].dtype
-        self.qkv = Linear(torch.cat([t.to(dt) for t in parts], dim=0))
-        self.o = Linear(tensors["o_proj.weight"])
+        self.qkv = Linear(torch.cat([t.to(dt) for t in parts], dim=0), self.ctx.num_sms)
+        self.o = Linear(tensors["o_proj.weight"], self.ctx.num_sms)
 
-    def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache) -> torch.Tensor:
+    def _project_out(self, out: torch.Tensor, residual: Optional[torch.Tensor]):
+        if residual is not None and self.o.add_into(out, residual):
+            return None
+        return self.o(out, out_dtype=self.ctx.dtype)
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache,
+                residual: Optional[torch.Tensor] = None):
+        """Returns the sublayer's output, or None when it was added into `residual`."""
         T = x.shape[0]
         g = step.groups[cache.group]
         qkv = self.qkv(x, out_dtype=self.ctx.dtype)
@@ -111,7 +119,7 @@ class GQAAttention(Mixer):
             tile_entry, tile_q0 = step.tiles[16]
             K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
                               self.Hq, self.Hkv, self.hd, self.scale, self.window)
-            return self.o(out, out_dtype=self.ctx.dtype)
+            return self._project_out(out, residual)
         if step.num_decode:
             splits = self._splits(step.num_decode, step.max_kv_len)
             K.attention_decode_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len,
@@ -121,7 +129,7 @@ class GQAAttention(Mixer):
         if tile_entry.numel():
             K.attention_prefill_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry,
                                      tile_tok0, self.Hq, self.Hkv, self.hd, self.scale, self.window)
-        return self.o(out, out_dtype=self.ctx.dtype)
+        return self._project_out(out, residual)
 
     def _splits(self, n_decode: int, max_kv_len: int) -> int:
         """Ranges each decoding request's keys are cut into, so that the grid fills the SMs

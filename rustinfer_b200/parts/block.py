@@ -53,10 +53,19 @@ class Block:
 
 
 def _pre_norm(block: Block, hidden: Hidden, step: StepContext, cache) -> None:
+    # a part that declares `adds_to_residual` may add its output into the stream itself
+    # (inside its last product's epilogue) and return None; otherwise the add rides on the
+    # next norm
     x = block.mixer_norm.add_norm(hidden.stream, hidden.pending)
-    hidden.pending = block.mixer.forward(x, step, cache)
+    if getattr(block.mixer, "adds_to_residual", False):
+        hidden.pending = block.mixer.forward(x, step, cache, residual=hidden.stream)
+    else:
+        hidden.pending = block.mixer.forward(x, step, cache)
     x = block.ffn_norm.add_norm(hidden.stream, hidden.pending)
-    hidden.pending = block.ffn.forward(x, step)
+    if getattr(block.ffn, "adds_to_residual", False):
+        hidden.pending = block.ffn.forward(x, step, residual=hidden.stream)
+    else:
+        hidden.pending = block.ffn.forward(x, step)
 
 
 ARRANGEMENTS: Dict[str, Callable] = {"pre_norm": _pre_norm}

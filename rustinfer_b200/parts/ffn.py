@@ -28,14 +28,30 @@ class SwiGLU(FeedForward):
                 "up_proj.weight": ParamDecl((self.inter, self.hidden)),
                 "down_proj.weight": ParamDecl((self.hidden, self.inter))}
 
+    adds_to_residual = True
+
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
-        self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0))
-        self.down = Linear(tensors["down_proj.weight"])
+        sms = self.ctx.num_sms
+        # bf16: rows alternate gate_j, up_j so that the product's epilogue can form
+        # silu(gate) * up; fp32: gate rows first, then up rows, for the separate kernel
+        self.paired = dt == torch.bfloat16 and self.hidden % 8 == 0 and g.is_cuda
+        if self.paired:
+            self.gate_up = Linear(torch.stack([g.to(dt), u.to(dt)], dim=1).reshape(2 * self.inter, self.hidden), sms)
+        else:
+            self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0), sms)
+        self.down = Linear(tensors["down_proj.weight"], sms)
 
-    def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        gu = self.gate_up(x, out_dtype=self.ctx.dtype)
-        m = torch.empty((x.shape[0], self.inter), dtype=self.ctx.dtype, device=x.device)
-        K.silu_mul(gu, m)
+    def forward(self, x: torch.Tensor, step: StepContext, residual: Optional[torch.Tensor] = None):
+        """Returns the sublayer's output, or None when it was added into `residual`."""
+        m = self.gate_up.silu_pairs(x) if self.paired else None
+        if m is None:
+            gu = self.gate_up(x, out_dtype=self.ctx.dtype)
+            if self.paired:                               # the fused path refused this input
+                gu = torch.cat([gu[:, 0::2], gu[:, 1::2]], dim=1).contiguous()
+            m = torch.empty((x.shape[0], self.inter), dtype=self.ctx.dtype, device=x.device)
+            K.silu_mul(gu, m)
+        if residual is not None and self.down.add_into(m, residual):
+            return None
         return self.down(m, out_dtype=self.ctx.dtype)

@@ -16,11 +16,18 @@ from ..ops import kernels as K
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, num_sms: int = 148):
         if weight.dim() != 2:
             raise ValueError("a linear weight is a matrix [out, in]")
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
+        self.num_sms = num_sms
+        # bf16 weights whose rows are 16-byte multiples run on this engine's tcgen05 kernel
+        self.tensor_core = (self.weight.dtype == torch.bfloat16 and self.weight.is_cuda
+                            and self.in_features % 8 == 0)
+
+    def _own(self, x: torch.Tensor) -> bool:
+        return self.tensor_core and x.dtype == torch.bfloat16 and x.is_contiguous() and x.data_ptr() % 16 == 0
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """x [M, in] -> [M, out] in `out_dtype` (default: x's dtype)."""
@@ -35,6 +42,27 @@ class Linear:
             return out if out_dtype == torch.float32 else out.to(out_dtype)
         if x.dtype != w.dtype:
             x = x.to(w.dtype)
+        if self._own(x) and out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype, device=x.device)
+            K.gemm_tc(x, w, out, K.EPI_BF16 if out_dtype == torch.bfloat16 else K.EPI_F32, num_sms=self.num_sms)
+            return out
         if out_dtype == w.dtype:
             return torch.mm(x, w.t())
         return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+    def add_into(self, x: torch.Tensor, residual: torch.Tensor) -> bool:
+        """residual (fp32 [M, out]) += x W^T inside the product's epilogue; False if this
+        weight cannot take that path (the caller then adds the product itself)."""
+        if not self._own(x) or residual.dtype != torch.float32 or not residual.is_contiguous():
+            return False
+        K.gemm_tc(x, self.weight, residual, K.EPI_RESIDUAL, num_sms=self.num_sms)
+        return True
+
+    def silu_pairs(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """For a weight whose rows alternate gate_j, up_j: silu(gate) * up, [M, out/2], fused
+        into the product's epilogue; None if this weight cannot take that path."""
+        if not self._own(x) or self.out_features % 2:
+            return None
+        out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
+        K.gemm_tc(x, self.weight, out, K.EPI_SILU, num_sms=self.num_sms)
+        return out

@@ -110,6 +110,77 @@ def test_gemm_f32_is_exact_fp32(M, N, K_):
     assert torch.allclose(out.double().cpu(), wide[:, 8: 8 + K_].double().cpu() @ w.double().cpu().T, atol=bound)
 
 
+TC_SHAPES = [(1, 130, 96), (8, 3072, 2048), (17, 544, 96), (64, 391, 272), (65, 391, 272), (300, 130, 104),
+             (200, 1000, 72), (128, 256, 64), (5, 16, 8)]
+
+
+@pytest.mark.parametrize("epi", ["bf16", "f32", "silu", "residual"])
+@pytest.mark.parametrize("M,N,K_", TC_SHAPES)
+def test_gemm_tc_against_float64(M, N, K_, epi):
+    """The tcgen05 kernel in both orientations (few tokens: weight on the 128-row side),
+    every epilogue, sizes that are no multiple of any tile."""
+    torch.manual_seed(M + N)
+    k = K()
+    if epi == "silu":
+        N -= N % 2                                      # gate/up pairs
+    x = torch.randn(M, K_).bfloat16().to(dev())
+    w = (torch.randn(N, K_) / math.sqrt(K_)).bfloat16().to(dev())
+    ref = x.double().cpu() @ w.double().cpu().T
+    if epi == "silu":
+        ref = P.swiglu(ref[:, 0::2], ref[:, 1::2])
+        out = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device=dev())
+        k.gemm_tc(x, w, out, k.EPI_SILU)
+        close(out, ref, torch.bfloat16)
+    elif epi == "residual":
+        base = torch.randn(M, N, device=dev())
+        out = base.clone()
+        k.gemm_tc(x, w, out, k.EPI_RESIDUAL)
+        close(out, ref + base.double().cpu(), torch.float32)
+    elif epi == "f32":
+        out = torch.full((M, N), float("nan"), device=dev())
+        k.gemm_tc(x, w, out, k.EPI_F32)
+        close(out, ref, torch.float32)
+    else:
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+        k.gemm_tc(x, w, out, k.EPI_BF16)
+        close(out, ref, torch.bfloat16)
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+
+
+@pytest.mark.parametrize("plan", [(1, 16, 1), (1, 16, 7), (1, 64, 3), (0, 16, 1), (0, 128, 2), (0, 256, 1), (0, 64, 5),
+                                  (1, 16, 1, 64), (1, 32, 1, 104), (1, 16, 3, 72)])
+def test_gemm_tc_plans_and_split_k(plan):
+    """Every tile width and orientation on one problem, with and without K slices; the
+    sliced result is the same bits whichever CTA finishes last (slices are added in order)."""
+    torch.manual_seed(7)
+    k = K()
+    M, N, K_ = 70, 300, 1032
+    x = torch.randn(M, K_).bfloat16().to(dev())
+    w = (torch.randn(N, K_) / math.sqrt(K_)).bfloat16().to(dev())
+    ref = x.double().cpu() @ w.double().cpu().T
+    outs = []
+    for _ in range(3):
+        out = torch.full((M, N), float("nan"), device=dev())
+        k.gemm_tc(x, w, out, k.EPI_F32, plan)
+        outs.append(out)
+    close(outs[0], ref, torch.float32)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+    # K slices of a product that is added into the fp32 stream add their parts one by one
+    base = torch.randn(M, N, device=dev())
+    h = base.clone()
+    k.gemm_tc(x, w, h, k.EPI_RESIDUAL, plan)
+    close(h, ref + base.double().cpu(), torch.float32)
+    # pairs of rows (gate, up) through SiLU, with tiles that cover fewer than 128 rows
+    out = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device=dev())
+    k.gemm_tc(x, w, out, k.EPI_SILU, plan)
+    close(out, P.swiglu(ref[:, 0::2], ref[:, 1::2]), torch.bfloat16)
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+
+
 def _rope_tables(positions, rot, theta=10000.0):
     f = P.rope_inv_freq(rot, theta, None)
     ang = torch.arange(positions, dtype=torch.float64)[:, None] * f[None, :]
