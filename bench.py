@@ -59,7 +59,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -78,6 +78,10 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self, windows):
+        # the timed regions are tens of milliseconds long and follow one another closely:
+        # every sample from the first region's start to the last one's end was taken under load
+        if windows:
+            windows = [(min(a for a, _ in windows), max(b for _, b in windows))]
         sm, mx, reasons = [], 0.0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for t, c in self.rows:

@@ -36,6 +36,9 @@ constexpr int KS = HD / 16;            // k-steps of Q*K^T
 constexpr int NT = HD / 8;             // n-tiles of the output
 constexpr int THREADS = 128;
 constexpr int MT = 64;                 // rows per prefill CTA
+// K/V tiles a decode CTA keeps in flight: decode is a pure stream of the cache, and what
+// bounds it is how many bytes every SM has on the way
+constexpr int DSTAGES = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -268,7 +271,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);            // [16][ROW]
-    bf16* KVs = Qs + 16 * ROW;                               // [2][K|V][KT][ROW]
+    bf16* KVs = Qs + 16 * ROW;                               // [DSTAGES][K|V][KT][ROW]
 
     const int slot = blockIdx.z;
     const int b = entry_list ? entry_list[slot] : slot;
@@ -287,8 +290,13 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int* bt = block_table + (size_t)b * table_stride;
 
-    if (t_begin < t_end) {
-        load_kv_tile(KVs, KVs + KT * ROW, cache, bt, t_begin * KT, lo, kvl, Hkv, kvh, page_size);
+    // prologue of the ring: tiles t_begin .. t_begin + DSTAGES - 2 (a group per tile, empty or not)
+#pragma unroll
+    for (int i = 0; i < DSTAGES - 1; ++i) {
+        if (t_begin + i < t_end) {
+            bf16* Kb = KVs + i * 2 * KT * ROW;
+            load_kv_tile(Kb, Kb + KT * ROW, cache, bt, (t_begin + i) * KT, lo, kvl, Hkv, kvh, page_size);
+        }
         cp_async_commit();
     }
     for (int c = tid; c < 16 * CH; c += THREADS) {
@@ -311,18 +319,19 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     const int kw0 = warp * 16;                                // this warp's 16 keys of every tile
 
     for (int t = t_begin; t < t_end; ++t) {
-        const int buf = (t - t_begin) & 1;
+        const int buf = (t - t_begin) % DSTAGES;
         bf16* Ks = KVs + buf * 2 * KT * ROW;
         bf16* Vs = Ks + KT * ROW;
-        if (t + 1 < t_end) {
-            bf16* Kn = KVs + (buf ^ 1) * 2 * KT * ROW;
-            load_kv_tile(Kn, Kn + KT * ROW, cache, bt, (t + 1) * KT, lo, kvl, Hkv, kvh, page_size);
+        cp_async_wait<DSTAGES - 2>();                         // tile t has landed (this thread's part)
+        __syncthreads();                                      // ... everyone's part; and tile t-1 is consumed
+        {
+            const int tn = t + DSTAGES - 1;                   // refill the buffer tile t-1 used
+            if (tn < t_end) {
+                bf16* Kn = KVs + ((tn - t_begin) % DSTAGES) * 2 * KT * ROW;
+                load_kv_tile(Kn, Kn + KT * ROW, cache, bt, tn * KT, lo, kvl, Hkv, kvh, page_size);
+            }
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
-        __syncthreads();
         if (t * KT + kw0 < kvl) {                             // the warp's keys are not all past the end
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -378,8 +387,9 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
                 mma_bf16(o[2 * np + 1], pa, vf[2], vf[3]);
             }
         }
-        __syncthreads();
     }
+    cp_async_wait<0>();
+    __syncthreads();
 
     // merge the four warps' states through shared memory (the K/V buffers are free now)
     float* Os = reinterpret_cast<float*>(KVs);               // [4][16][HD]
@@ -455,7 +465,7 @@ __global__ void combine_kernel(const float* __restrict__ part_o, const float* __
 }
 
 constexpr size_t PREFILL_SMEM = ((size_t)MT * ROW + 4 * (size_t)KT * ROW) * sizeof(bf16);
-constexpr size_t DECODE_SMEM_KV = 4 * (size_t)KT * ROW * sizeof(bf16);
+constexpr size_t DECODE_SMEM_KV = 2 * (size_t)DSTAGES * KT * ROW * sizeof(bf16);
 constexpr size_t DECODE_SMEM_MERGE = (4 * 16 * (size_t)HD + 128) * sizeof(float);
 constexpr size_t DECODE_SMEM = 16 * (size_t)ROW * sizeof(bf16) +
                                (DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE);

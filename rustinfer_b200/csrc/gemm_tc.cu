@@ -99,13 +99,22 @@ __device__ __forceinline__ void tmem_ld16(unsigned addr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+constexpr int MAX_STAGES = 32;
+// bytes of operand stages per CTA: few tokens (a pure weight stream) take half an SM's
+// shared memory, so that the next product's CTAs can move in and prefetch beside them
+constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET_STREAM = 96 * 1024;
+int g_stream_budget = SMEM_BUDGET_STREAM;
+// The MMA always reads 128 rows of A; when a tile loads fewer, the rows past them are
+// whatever follows in shared memory, and the lanes they feed are never stored.  The slack
+// keeps that read inside the allocation.
+constexpr int SMEM_TAIL = BM * BK * 2;
+constexpr size_t SMEM_EXTRA = SMEM_TAIL + 1024 /*alignment*/ + 1024 /*barriers*/;
+constexpr size_t SMEM_TOTAL = (size_t)SMEM_BUDGET + SMEM_EXTRA;
+
 template <int BN> struct Cfg {
-    static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
-    static constexpr int STAGES_FIT = (200 * 1024) / STAGE_BYTES;
-    static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
     static constexpr int ACC_COLS = BN < 32 ? 32 : BN;      // columns of one accumulator
     static constexpr int TMEM_COLS = 2 * ACC_COLS;          // two accumulators: epilogue and MMA overlap
-    static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 struct Params {
@@ -122,6 +131,8 @@ struct Params {
     int* error;
     int tiles_a, n_tiles;
     int a_box;                           // rows of A per tile actually loaded (<= 128, a multiple of 8)
+    int stages, stage_bytes;             // ring of operand stages: (a_box + BN) * 128 bytes each
+    int budget;                          // bytes of the ring
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
@@ -198,16 +209,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 
 // Persistent over tiles: CTA x takes tiles x, x + gridDim.x, ...; blockIdx.z is the K slice.
 template <int BN>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const Params p) {
     using C = Cfg<BN>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);      // swizzle atoms are 1 KiB
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)C::STAGES * C::STAGE_BYTES);
-    uint64_t* empty = full + C::STAGES;
-    uint64_t* acc_full = empty + C::STAGES;              // [2] accumulator written, epilogue may read
+    const int STAGES = p.stages, STAGE_BYTES = p.stage_bytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.budget + SMEM_TAIL);
+    uint64_t* empty = full + MAX_STAGES;
+    uint64_t* acc_full = empty + MAX_STAGES;             // [2] accumulator written, epilogue may read
     uint64_t* acc_empty = acc_full + 2;                  // [2] accumulator read, MMA may overwrite
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
     int* ticket_slot = reinterpret_cast<int*>(tmem_slot + 1);
@@ -220,7 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int n_kb = max(kb_end - kb_begin, 0);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -240,16 +252,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // earlier kernel writes weights, so they stream in while the predecessor drains.
         const CUtensorMap* wmap = p.swap ? &map_a : &map_b;
         const CUtensorMap* xmap = p.swap ? &map_b : &map_a;
-        const int woff = p.swap ? 0 : BM * BK * 2, xoff = p.swap ? BM * BK * 2 : 0;
+        const int woff = p.swap ? 0 : p.a_box * BK * 2, xoff = p.swap ? p.a_box * BK * 2 : 0;
         const unsigned stage_tx = (unsigned)(p.a_box + BN) * BK * 2;   // bytes the two boxes of a stage bring
         pdl_trigger();
-        const int pre = blockIdx.x < p.n_tiles ? min(n_kb, C::STAGES) : 0;
+        const int pre = blockIdx.x < p.n_tiles ? min(n_kb, STAGES) : 0;
         {
             const int tile = blockIdx.x;
             const int w0 = p.swap ? (tile % p.tiles_a) * p.a_box : (tile / p.tiles_a) * BN;
             for (int i = 0; i < pre; ++i) {
                 mbar_expect_tx(&full[i], stage_tx);
-                tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + woff, wmap, &full[i], (kb_begin + i) * BK, w0);
+                tma_load_2d(tiles + (size_t)i * STAGE_BYTES + woff, wmap, &full[i], (kb_begin + i) * BK, w0);
             }
         }
         pdl_wait();
@@ -259,8 +271,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
             const int w0 = p.swap ? a0 : b0, x0 = p.swap ? b0 : a0;
             for (int i = 0; i < n_kb; ++i, ++it) {
-                const int s = it % C::STAGES, round = it / C::STAGES;
-                unsigned char* st = tiles + (size_t)s * C::STAGE_BYTES;
+                const int s = it % STAGES, round = it / STAGES;
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                 if (it >= pre) {
                     if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, p.error, ERR_PRODUCER_WAIT)) { ok = false; break; }
                     mbar_expect_tx(&full[s], stage_tx);
@@ -282,11 +294,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             const unsigned tmem_d = tmem_base + buf * C::ACC_COLS;
             for (int i = 0; i < n_kb; ++i, ++it) {
-                const int s = it % C::STAGES, round = it / C::STAGES;
+                const int s = it % STAGES, round = it / STAGES;
                 if (!mbar_wait(&full[s], round & 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
                 tc_fence_after();
-                const unsigned sa = smem_u32(tiles + (size_t)s * C::STAGE_BYTES);
-                const unsigned sb = sa + BM * BK * 2;
+                const unsigned sa = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                const unsigned sb = sa + p.a_box * BK * 2;
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)
                     mma_bf16_ss(tmem_d, smem_desc(sa + k * 32), smem_desc(sb + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
@@ -296,7 +308,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (!ok) {
             // whatever was loaded last must have landed before shared memory is given up
-            for (int s = 0; s < C::STAGES; ++s)
+            for (int s = 0; s < STAGES; ++s)
                 for (int par = 0; par < 2; ++par)
                     if (mbar_try_wait(&full[s], par)) break;
             for (unsigned spin = 0; spin < 4096; ++spin) __nanosleep(256);
@@ -461,7 +473,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int ti
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)Cfg<BN>::SMEM);
+                                             (int)SMEM_TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -473,7 +485,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int ti
     }
     // one CTA per SM walks the tiles; with K slices every CTA has exactly one tile
     const int ctas = (p.splits > 1 || tiles < sms) ? tiles : sms;
-    RI_CHECKED(ri_launch(gemm_tc_kernel<BN>, dim3(ctas, 1, p.splits), dim3(THREADS), Cfg<BN>::SMEM, s, ma, mb, p));
+    RI_CHECKED(ri_launch(gemm_tc_kernel<BN>, dim3(ctas, 1, p.splits), dim3(THREADS), (size_t)p.budget + SMEM_EXTRA, s, ma, mb, p));
     return ri_launch_status();
 }
 }  // namespace
@@ -494,6 +506,11 @@ RI_API long long ri_gemm_tc_workspace_floats(int M, int N, int splits, int swap,
 // tile, zero before the first call (the kernel leaves them zero).  error: one int that a
 // timed-out wait sets; zero it before use and read it when in doubt.
 RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }
+
+// Bytes of operand stages a CTA keeps when few tokens stream the weights (16 KiB to 200 KiB).
+RI_API void ri_gemm_tc_set_stream_budget(int bytes) {
+    if (bytes >= 16 * 1024 && bytes <= SMEM_BUDGET) g_stream_budget = bytes & ~1023;
+}
 
 // a_box: rows of the 128-row operand a tile really covers (a multiple of 8 from 8 to 128;
 // fewer than 128 evens out the last wave of tiles over the SMs).
@@ -518,6 +535,10 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     p.vec = ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && ((size_t)ld_out * esize) % 16 == 0) ? 1 : 0;
     CUtensorMap ma, mb;
     p.a_box = a_box;
+    p.stage_bytes = (a_box + bn) * BK * 2;
+    p.budget = (swap && bn <= 64) ? g_stream_budget : SMEM_BUDGET;
+    p.stages = p.budget / p.stage_bytes;
+    if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
     p.tiles_a = (p.a_rows + a_box - 1) / a_box;
     p.n_tiles = p.tiles_a * tiles_b;
     int st = make_map(A, p.a_rows, K, a_box, &ma);

@@ -90,7 +90,13 @@ def attention_plain(head_dim: int) -> ctypes.CDLL:
 
 
 def gemm_tc() -> ctypes.CDLL:
-    return _load("ri_gemm_tc", ["gemm_tc.cu"])
+    lib = _load("ri_gemm_tc", ["gemm_tc.cu"])
+    kb = os.environ.get("RUSTINFER_B200_STREAM_KB")
+    if kb and not getattr(lib, "_budget_set", False):
+        lib.ri_gemm_tc_set_stream_budget.argtypes = [_I]
+        lib.ri_gemm_tc_set_stream_budget(int(kb) * 1024)
+        lib._budget_set = True
+    return lib
 
 
 MMA_MAX_HEAD_DIM = 256

@@ -132,13 +132,13 @@ class GQAAttention(Mixer):
         return self._project_out(out, residual)
 
     def _splits(self, n_decode: int, max_kv_len: int) -> int:
-        """Ranges each decoding request's keys are cut into, so that the grid fills the SMs
-        about twice over; never more ranges than 64-key tiles."""
+        """Ranges each decoding request's keys are cut into, so that about three CTAs sit on
+        every SM (each keeps several K/V tiles in flight); never more ranges than 64-key tiles."""
         chunks = (self.Hq // self.Hkv + 15) // 16
         ctas = n_decode * self.Hkv * chunks
         span = min(max_kv_len, self.window) if self.window else max_kv_len
         tiles = max(1, (span + 63) // 64)
-        want = -(-2 * self.ctx.num_sms // ctas)
+        want = -(-3 * self.ctx.num_sms // ctas)
         return max(1, min(want, tiles, self.MAX_SPLITS))
 
     def _q_only(self, qkv: torch.Tensor) -> torch.Tensor:
