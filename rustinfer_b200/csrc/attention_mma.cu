@@ -75,6 +75,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
                                              const int* __restrict__ bt, int k0, int k_lo, int k_hi,
                                              int Hkv, int kvh, int page_size) {
     const size_t head_step = (size_t)page_size * HD;
+    const int shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;   // power of two: no division
     for (int c = threadIdx.x; c < KT * CH; c += THREADS) {
         const int kk = c / CH, ch = c - kk * CH;
         const int key = k0 + kk;
@@ -82,7 +83,8 @@ __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __r
         const bf16* sk = cache;
         const bf16* sv = cache;
         if (ok) {
-            const int page = bt[key / page_size], off = key % page_size;
+            const int blk = shift >= 0 ? key >> shift : key / page_size;
+            const int page = bt[blk], off = key - blk * page_size;
             sk = cache + ((size_t)(page * 2) * Hkv + kvh) * head_step + (size_t)off * HD + ch * 8;
             sv = sk + (size_t)Hkv * head_step;
         }
@@ -150,6 +152,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         lo_row[i] = window > 0 ? max(0, p_row[i] - window + 1) : 0;
     }
 
+    const int p_warp_first = p_first + (warp * 16) / Gc;     // position of the warp's first row
     unsigned qf[KS][4];
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks)
@@ -187,17 +190,27 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                 mma_bf16(s[2 * np + 1], qf[ks], kf[2], kf[3]);
             }
         }
+        // Scores stay unscaled; the scale rides on the exponent: p = 2^(s*scale - m).  Only
+        // tiles that reach past the warp's first row (the diagonal) or a window need masks.
         const int key0 = t * KT + (lane & 3) * 2;
         float mx[2] = {-INFINITY, -INFINITY};
+        if (window > 0 || t * KT + KT - 1 > p_warp_first) {
 #pragma unroll
-        for (int n = 0; n < KT / 8; ++n) {
+            for (int n = 0; n < KT / 8; ++n) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = key0 + n * 8 + (e & 1);
-                const int i = e >> 1;
-                const bool seen = ok_row[i] && key <= p_row[i] && key >= lo_row[i];
-                s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
-                mx[i] = fmaxf(mx[i], s[n][e]);
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + n * 8 + (e & 1);
+                    const int i = e >> 1;
+                    const bool seen = ok_row[i] && key <= p_row[i] && key >= lo_row[i];
+                    s[n][e] = seen ? s[n][e] : -INFINITY;
+                    mx[i] = fmaxf(mx[i], s[n][e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int n = 0; n < KT / 8; ++n) {
+                mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
             }
         }
         float alpha[2], muse[2];
@@ -205,7 +218,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         for (int i = 0; i < 2; ++i) {
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
             mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
-            const float mnew = fmaxf(m[i], mx[i]);
+            const float mnew = fmaxf(m[i], mx[i] * scale_log2);       // m is kept in scaled units
             muse[i] = mnew == -INFINITY ? 0.f : mnew;
             alpha[i] = exp2f(m[i] - muse[i]);
             m[i] = mnew;
@@ -220,7 +233,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         for (int n = 0; n < KT / 8; ++n) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                s[n][e] = exp2f(s[n][e] - muse[e >> 1]);
+                s[n][e] = exp2f(fmaf(s[n][e], scale_log2, -muse[e >> 1]));
                 l[e >> 1] += s[n][e];
             }
         }

@@ -38,10 +38,31 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
     const int row_id = blockIdx.y;
     const float* row = logits + (size_t)row_id * ld;
     unsigned long long mine = 0ull;                      // (ordered logit << 32) | ~index
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
-        const unsigned long long key =
-            ((unsigned long long)ordered_bits(row[i]) << 32) | (unsigned int)(0xffffffffu - (unsigned int)i);
-        mine = key > mine ? key : mine;
+    const int stride = gridDim.x * blockDim.x, first = blockIdx.x * blockDim.x + threadIdx.x;
+    if ((ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        const int n4 = vocab >> 2;                       // 16-byte loads over the aligned part of the row
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i = first; i < n4; i += stride) {
+            const float4 v = row4[i];
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const unsigned long long key = ((unsigned long long)ordered_bits(e[k]) << 32) |
+                                               (unsigned int)(0xffffffffu - (unsigned int)(4 * i + k));
+                mine = key > mine ? key : mine;
+            }
+        }
+        for (int i = 4 * n4 + first; i < vocab; i += stride) {
+            const unsigned long long key =
+                ((unsigned long long)ordered_bits(row[i]) << 32) | (unsigned int)(0xffffffffu - (unsigned int)i);
+            mine = key > mine ? key : mine;
+        }
+    } else {
+        for (int i = first; i < vocab; i += stride) {
+            const unsigned long long key =
+                ((unsigned long long)ordered_bits(row[i]) << 32) | (unsigned int)(0xffffffffu - (unsigned int)i);
+            mine = key > mine ? key : mine;
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {

@@ -132,14 +132,19 @@ class GQAAttention(Mixer):
         return self._project_out(out, residual)
 
     def _splits(self, n_decode: int, max_kv_len: int) -> int:
-        """Ranges each decoding request's keys are cut into, so that about three CTAs sit on
-        every SM (each keeps several K/V tiles in flight); never more ranges than 64-key tiles."""
+        """Ranges each decoding request's keys are cut into.  About three CTAs sit on an SM
+        (each keeps several K/V tiles in flight), so the grid should be a whole number of
+        such waves: among the candidates the one whose last wave is fullest wins, fewer
+        ranges on a tie; never more ranges than 64-key tiles."""
         chunks = (self.Hq // self.Hkv + 15) // 16
         ctas = n_decode * self.Hkv * chunks
         span = min(max_kv_len, self.window) if self.window else max_kv_len
         tiles = max(1, (span + 63) // 64)
-        want = -(-3 * self.ctx.num_sms // ctas)
-        return max(1, min(want, tiles, self.MAX_SPLITS))
-
-    def _q_only(self, qkv: torch.Tensor) -> torch.Tensor:
-        return qkv[:, : self.Hq * self.hd]
+        slots = 3 * self.ctx.num_sms
+        best, best_eff = 1, -1.0
+        for s in range(1, min(tiles, self.MAX_SPLITS) + 1):
+            waves = ctas * s / slots
+            eff = waves / max(1.0, float(-(-ctas * s // slots)))     # below one wave: the share of slots used
+            if eff > best_eff + 0.02:
+                best, best_eff = s, eff
+        return best
