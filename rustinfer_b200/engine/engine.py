@@ -112,8 +112,7 @@ class Engine:
         entries = []
         samplers: List[Request] = []
         for e in plan.entries:
-            seq = e.request.sequence
-            entries.append(StepEntry(e.request.request_id, seq[e.start: e.start + e.count],
+            entries.append(StepEntry(e.request.request_id, e.request.tokens(e.start, e.count),
                                      [e.count - 1] if e.samples else []))
             if e.samples:
                 samplers.append(e.request)

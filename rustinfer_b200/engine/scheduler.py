@@ -54,6 +54,15 @@ class Request:
     def sequence(self) -> List[int]:
         return self.prompt + self.output
 
+    def tokens(self, start: int, count: int) -> List[int]:
+        """Tokens start .. start+count-1 of prompt + output, without joining the two lists."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n: start - n + count]
+        if start + count <= n:
+            return self.prompt[start: start + count]
+        return self.prompt[start:] + self.output[: start + count - n]
+
     @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed
