@@ -107,7 +107,8 @@ class GQAAttention(Mixer):
         qkv = self.qkv(x, out_dtype=self.ctx.dtype)
         writes = self.own_kv and cache.writes
         if self.position is not None:
-            K.rope_scatter(qkv if writes else self._q_only(qkv), step.positions, self.position.cos,
+            # a layer that reads another's cache has only the q projection: qkv is q alone
+            K.rope_scatter(qkv, step.positions, self.position.cos,
                            self.position.sin, g.slot_of_token if writes else None,
                            cache.kv if writes else None, self.Hq, self.Hkv if writes else 0, self.hd,
                            self.position.rotary_dim)

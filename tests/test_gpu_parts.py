@@ -268,3 +268,97 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
     assert r.cache.slot("c") == 0
     lg = r.step([StepEntry("c", b, list(range(len(b))))])
     assert rel_err(lg, _toy_plain(cfg, w, b)) <= tol
+
+
+# ------------------------------------------- run order as data, shared caches, windows
+# A toy architecture out of the framework's own parts, arranged in ways Llama never is:
+# a layer with a sliding window (its pages form a cache group of their own and are given
+# back as the window passes), a layer that runs twice (each visit has its own cache), and
+# a layer without key/value projections that reads the cache another visit wrote.
+
+def _register_arranged():
+    from rustinfer_b200.config.registry import ArchitectureFamily, register_architecture
+    from rustinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+    def spec_of(cfg):
+        d, hd, Hq, Hkv = cfg["hidden_size"], 16, cfg["hidden_size"] // 16, 2
+        norm = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+        ffn = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": cfg["intermediate_size"]})
+        rope = PartSpec("rope", {"head_dim": hd, "rotary_dim": hd, "theta": 10000.0, "scaling": None})
+        att = lambda window, own: PartSpec("gqa_attention", {
+            "hidden_size": d, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd, "scale": 0.25,
+            "window": window, "position": rope, "own_kv": own})
+        kinds = [att(None, True), att(cfg["window"], True), att(None, False)]
+        layers = tuple(LayerSpec(mixer=m, mixer_norm=norm, ffn=ffn, ffn_norm=norm,
+                                 names={"mixer": f"l{i}.att.", "mixer_norm": f"l{i}.n1.", "ffn": f"l{i}.mlp.",
+                                        "ffn_norm": f"l{i}.n2."}) for i, m in enumerate(kinds))
+        # layer 0 (full), layer 1 (window), layer 0 again, layer 2 reading the cache of the first visit
+        order = (RunEntry(0), RunEntry(1), RunEntry(0), RunEntry(2, cache_of=0))
+        return ModelSpec(hidden_size=d, vocab_size=cfg["vocab_size"], layers=layers, run_order=order,
+                         final_norm=norm, embed_name="embed.", final_norm_name="norm.", head_name="head.",
+                         tie_head=False)
+
+    register_architecture(["ArrangedToyLM"], ArchitectureFamily("arranged", lambda c, g: dict(c), spec_of))
+
+
+def _arranged_plain(cfg, w, ids):
+    d, hd, Hkv = cfg["hidden_size"], 16, 2
+    Hq, T = d // hd, len(ids)
+    f = P.rope_inv_freq(hd, 10000.0, None)
+    pos = torch.arange(T)
+    h = P.embedding(w["embed.weight"], ids)
+    kv_of_visit = {}
+    for visit, (layer, cache_of) in enumerate([(0, None), (1, None), (0, None), (2, 0)]):
+        p = f"l{layer}."
+        x = P.rmsnorm(h, w[p + "n1.weight"], 1e-5)
+        q = P.rope_rotate((x @ w[p + "att.q_proj.weight"].T).view(T, Hq, hd), pos, f)
+        if cache_of is None:
+            k = P.rope_rotate((x @ w[p + "att.k_proj.weight"].T).view(T, Hkv, hd), pos, f)
+            v = (x @ w[p + "att.v_proj.weight"].T).view(T, Hkv, hd)
+            kv_of_visit[visit] = (k, v)
+        else:
+            k, v = kv_of_visit[cache_of]
+        a = P.causal_gqa_attention(q, k, v, 0.25, cfg["window"] if layer == 1 else None).reshape(T, d)
+        h = h + a @ w[p + "att.o_proj.weight"].T
+        x = P.rmsnorm(h, w[p + "n2.weight"], 1e-5)
+        m = P.swiglu(x @ w[p + "mlp.gate_proj.weight"].T, x @ w[p + "mlp.up_proj.weight"].T)
+        h = h + m @ w[p + "mlp.down_proj.weight"].T
+    return P.rmsnorm(h, w["norm.weight"], 1e-5) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_run_order_shared_cache_and_window_group(tmp_path, dtype):
+    from rustinfer_b200.engine.runner import ModelRunner, StepEntry
+    from rustinfer_b200.parts.base import PagedKV
+    from rustinfer_b200.weights.random_init import write_random_model
+    _register_arranged()
+    cfg = {"architectures": ["ArrangedToyLM"], "hidden_size": 64, "intermediate_size": 96, "vocab_size": 113,
+           "window": 11}
+    folder = write_random_model(str(tmp_path / "arranged"), cfg, seed=3, std=0.2, norm_std=0.2)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    _, w = P.read_model_folder(folder)
+    assert "l2.att.k_proj.weight" not in w                    # the reading layer projects no keys
+    r = ModelRunner(folder, dtype=dtype, max_model_len=128, page_size=4, num_pages=40, max_batch_seqs=2,
+                    max_batch_tokens=128)
+    # two cache groups: full attention (visits 0 and 2 of the run order) and the window layer
+    assert [g.need for g in r.layout.groups] == [PagedKV(2, 16, None), PagedKV(2, 16, 11)]
+    assert r.layout.groups[0].entries == [0, 2] and r.layout.groups[1].entries == [1]
+    assert r.layout.entry_cache == [(0, 0), (1, 0), (0, 1), (0, 0)] and r.layout.entry_writes[3] is False
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 113, (60,), generator=g).tolist()
+    ref = _arranged_plain(cfg, w, ids)
+    tol = 2e-5 if dtype == "float32" else 4e-2
+    for cuts in ([60], [7, 20, 1, 1, 1, 2, 28], [1] * 60):
+        r.open("a")
+        outs, at = [], 0
+        for c in cuts:
+            outs.append(r.step([StepEntry("a", ids[at: at + c], list(range(c)))]))
+            at += c
+            held = r.cache.pages_held("a")
+            assert held[0] == (at + 3) // 4                        # every key is kept
+            assert held[1] <= (11 + 4 + 3) // 4 + 1                # the window group holds a window's worth
+        assert rel_err(torch.cat(outs), ref) <= tol, cuts
+        r.close("a")
+        r.cache.check_invariants()
+    assert r.cache.free_pages() == {0: 40, 1: 40}
