@@ -202,7 +202,40 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, int vpad,
     __syncthreads();
     if (tid == 0) out[r] = (int)(0xffffffffu - (unsigned int)(s[found] & 0xffffffffu));
 }
+// ------------------------------------------------------- stop check and token feedback
+// After the tokens of a decode step are chosen: per row, count the token, decide whether the
+// request stops (a stop id unless ignored, or generated >= max_tokens; the host twin of this
+// rule is crates/infer-core/src/ports/pipeline_ops.rs:117-120), and put the token where the
+// next step reads its input ids, so that the next step can start before the host has seen
+// anything.  slot_state[slot] = {generated, max_tokens, ignore_eos, last_token}.
+__global__ void decode_feedback_kernel(const int* __restrict__ sampled, const int* __restrict__ state_slots,
+                                       int rows, int* __restrict__ slot_state, const int* __restrict__ eos_ids,
+                                       int n_eos, int* __restrict__ result, int* __restrict__ token_feed) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    const int tok = sampled[r];
+    int* st = slot_state + 4 * state_slots[r];
+    const int generated = st[0] + 1;
+    bool stop = generated >= st[1];
+    if (!st[2])
+        for (int e = 0; e < n_eos; ++e) stop = stop || tok == eos_ids[e];
+    st[0] = generated;
+    st[3] = tok;
+    result[r] = tok;                                      // [rows] tokens, then [rows] stop flags
+    result[rows + r] = stop ? 1 : 0;
+    if (token_feed) token_feed[r] = tok;
+}
 }  // namespace
+
+RI_API int ri_decode_feedback(const int* sampled, const int* state_slots, int rows, int* slot_state,
+                              const int* eos_ids, int n_eos, int* result, int* token_feed, void* stream) {
+    if (rows <= 0) return 0;
+    RI_CHECKED(ri_launch(decode_feedback_kernel, dim3((rows + 127) / 128), dim3(128), 0, (cudaStream_t)stream,
+                         sampled, state_slots, rows, slot_state, eos_ids, n_eos, result, token_feed));
+    return ri_launch_status();
+}
 
 // state: rows 64-bit words, count: rows 32-bit words, both zero before the first call (the
 // kernel leaves them zero).  Calls that share them must not overlap on the GPU.

@@ -22,7 +22,8 @@ from ..config.run_config import DEFAULT_CAPTURE_SIZES, RunConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, fresh_seed
 from .runner import ModelRunner, StepEntry
-from .scheduler import Request, Scheduler
+from ..ops import kernels as K
+from .scheduler import FINISHED, Request, Scheduler
 
 
 @dataclass
@@ -42,7 +43,17 @@ class StepOutput:
 
 
 @dataclass
+class _InFlight:
+    plan: Any
+    samplers: List[Request]
+    turn: int                           # which result buffer its tokens land in
+    event: Any
+    lazy: bool                          # all rows greedy: its tokens may be read after the next launch
+
+
+@dataclass
 class EngineStats:
+    stop_flag_mismatches: int = 0
     steps: int = 0
     prompt_tokens: int = 0
     generated_tokens: int = 0
@@ -74,6 +85,14 @@ class Engine:
         self._requests: Dict[int, Request] = {}
         self.stats = EngineStats()
         self._next_id = 0
+        # the step in flight, the device buffers its tokens and stop flags land in (two, used
+        # in turn, with pinned host twins), and the buffer the next step reads its ids from
+        self._inflight: Optional[_InFlight] = None
+        self._turn = 0
+        dev = self.runner.device
+        self._result_dev = [torch.zeros(2 * max_batch_seqs, dtype=torch.int32, device=dev) for _ in range(2)]
+        self._result_host = [torch.zeros(2 * max_batch_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._feed = torch.zeros(max_batch_seqs, dtype=torch.int32, device=dev)
 
     @classmethod
     def from_run_config(cls, cfg: RunConfig) -> "Engine":
@@ -98,41 +117,102 @@ class Engine:
         return req.request_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
+    # ---------------------------------------------------------------------------- step
     def step(self) -> List[StepOutput]:
-        """One iteration: schedule a batch, run it, sample.  Returns what each request that
-        produced a token in this step got (token ids on the host)."""
+        """One iteration: schedule a batch, launch it, choose tokens on the device.
+
+        A step whose rows are all greedy leaves its tokens on the device (`_inflight`): the
+        stop check runs there, the tokens are fed to the next step there, and the host reads
+        them only after it has launched that next step, so planning and launching overlap
+        the GPU's work.  The tokens a call returns are therefore those of the step before
+        the one it launched; `has_unfinished()` stays true until the last ones are read.
+        This is the engine's counterpart of RustInfer's one-deep device-resident decode
+        pipeline (crates/infer-worker/src/application/runtime/abc_decode.rs:77-89,109-)."""
         sched = self.scheduler
+        outs: List[StepOutput] = []
         before = sched.num_preemptions
         plan = sched.schedule()
         self.stats.preemptions += sched.num_preemptions - before
+        chain = self._inflight is not None and self._chainable(plan)
+        if self._inflight is not None and not chain:
+            outs += self._resolve()                           # the plan needs these tokens on the host
+            plan.entries = [e for e in plan.entries if e.request.state != FINISHED]
         if not plan.entries:
-            return []
-        entries = []
+            return outs
+        r = self.runner
+        entries: List[StepEntry] = []
         samplers: List[Request] = []
         for e in plan.entries:
-            entries.append(StepEntry(e.request.request_id, e.request.tokens(e.start, e.count),
-                                     [e.count - 1] if e.samples else []))
+            req = e.request
+            if e.start == 0:                                  # first portion since (re)admission
+                made = len(req.output)
+                cap = min(req.params.max_tokens, r.max_model_len - len(req.prompt))
+                r.set_request_limits(req.request_id, made, cap, req.params.ignore_eos)
+            toks = [0] if chain else req.tokens(e.start, e.count)
+            entries.append(StepEntry(req.request_id, toks, [e.count - 1] if e.samples else []))
             if e.samples:
-                samplers.append(e.request)
+                samplers.append(req)
         t0 = time.perf_counter()
-        logits = self.runner.step(entries, borrow_logits=True)
-        sampled: List[int] = []
+        logits = r.step(entries, device_tokens=self._feed if chain else None, borrow_logits=True)
+        launched = None
         if samplers:
-            sampled = self.sampler.sample(
-                logits, [q.params for q in samplers], [q.seed for q in samplers],
-                [len(q.prompt) + len(q.output) for q in samplers])
-        self.stats.step_ms.append((time.perf_counter() - t0) * 1e3)
+            n = len(samplers)
+            positions = [len(q.prompt) + len(q.output) + q.undelivered for q in samplers]
+            chosen = self.sampler.sample_device(logits, [q.params for q in samplers],
+                                                [q.seed for q in samplers], positions)
+            k = self._turn = (self._turn + 1) % 2
+            K.decode_feedback(chosen, r.last_want_slots, r.slot_state, r.eos_dev, self._result_dev[k], self._feed)
+            self._result_host[k][: 2 * n].copy_(self._result_dev[k][: 2 * n], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            launched = _InFlight(plan, samplers, k, ev, all(q.params.is_greedy() for q in samplers))
+        sched.advance(plan)
         self.stats.steps += 1
         self.stats.prompt_tokens += sum(e.count for e in plan.entries) - sum(
-            1 for e in plan.entries if e.count == 1 and e.request.output)
-        self.stats.generated_tokens += len(sampled)
-        sched.complete_step(plan, sampled)
-        return [StepOutput(q.request_id, t, q.finish_reason) for q, t in zip(samplers, sampled)]
+            1 for e in plan.entries if e.count == 1 and (e.request.output or e.request.undelivered > 1))
+        if chain:
+            outs += self._resolve()                           # last step's tokens, read while this one runs
+        self._inflight = launched
+        if launched is not None and not launched.lazy:
+            outs += self._resolve()
+        self.stats.step_ms.append((time.perf_counter() - t0) * 1e3)
+        return outs
+
+    def _chainable(self, plan) -> bool:
+        """The planned step can take its input tokens from the device: it is made of the
+        very rows whose tokens are in flight, one token each, in the same order."""
+        prev = self._inflight
+        if not prev.lazy or len(plan.entries) != len(prev.samplers) or not plan.entries:
+            return False
+        return all(e.count == 1 and e.samples and e.request is q and q.params.is_greedy()
+                   for e, q in zip(plan.entries, prev.samplers))
+
+    def _resolve(self) -> List[StepOutput]:
+        """Wait for the tokens of the step in flight, hand them to the scheduler."""
+        f, self._inflight = self._inflight, None
+        f.event.synchronize()
+        n = len(f.samplers)
+        res = self._result_host[f.turn][: 2 * n].tolist()
+        tokens, stops = res[:n], res[n:]
+        live = [q.state != FINISHED for q in f.samplers]
+        self.scheduler.deliver(f.plan, tokens)
+        outs = []
+        for q, t, s, was_live in zip(f.samplers, tokens, stops, live):
+            if not was_live:
+                continue
+            # the device's stop flag and the host's decision are the same rule twice
+            if bool(s) != (q.finish_reason in ("stop", "length")):
+                self.stats.stop_flag_mismatches += 1
+            outs.append(StepOutput(q.request_id, t, q.finish_reason))
+        self.stats.generated_tokens += len(outs)
+        return outs
 
     def abort(self, request_id: int) -> None:
         """Stop a request wherever it is; its pages and slot are given back."""
+        if self._inflight is not None:
+            self._resolve()
         q = self._requests.pop(request_id)
         self.scheduler.abort(q)
 
@@ -153,9 +233,11 @@ class Engine:
             raise ValueError("one SamplingParams for all prompts, or one per prompt")
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         t0 = time.perf_counter()
-        while self.scheduler.has_work():
-            if not self.step() and not self.scheduler.has_work():
-                break
+        idle = 0
+        while self.has_unfinished() and idle < 4:
+            steps_before = self.stats.steps
+            got = self.step()
+            idle = 0 if (got or self.stats.steps != steps_before) else idle + 1
         self.stats.seconds += time.perf_counter() - t0
         self.runner.check_kernel_errors()
         return [self.take_finished(i) for i in ids]

@@ -238,11 +238,16 @@ class ModelRunner:
         self.tile_rows = self.model.attention_tile_rows()
         self.prefill_tile_rows = self.model.prefill_tile_rows()
         cap_t, cap_b = self.max_batch_tokens, self.max_batch_seqs
-        n_ints = 4 * cap_t + 5 * cap_b + 64
+        n_ints = 5 * cap_t + 5 * cap_b + 64
         n_ints += len(paged) * (cap_b * self.max_pages_per_request + cap_t + 16)
         for r in self.tile_rows + self.prefill_tile_rows:
             n_ints += 2 * (cap_t // r + cap_b + 8)
         self._staging = _Staging(n_ints, self.device)
+        # per-request counters the device keeps by state slot: {generated, max_tokens, ignore_eos, last_token}
+        self.slot_state = torch.zeros((self.max_batch_seqs, 4), dtype=torch.int32, device=self.device)
+        eos = [t for t in self.spec.eos_token_ids if 0 <= t < self.spec.vocab_size]
+        self.eos_dev = torch.tensor(eos, dtype=torch.int32, device=self.device) if eos else None
+        self.last_want_slots: Optional[torch.Tensor] = None   # state slot of every wanted row of the last step
         self.steps_run = 0
         self.h2d_bytes_last = 0
         self.graph_replays = 0
@@ -305,6 +310,12 @@ class ModelRunner:
     def open(self, request_id: Any) -> None:
         self.cache.open(request_id)
 
+    def set_request_limits(self, request_id: Any, generated: int, max_tokens: int, ignore_eos: bool) -> None:
+        """What the device-side stop check knows of a request: tokens generated so far, the
+        count at which it stops, whether stop ids are ignored."""
+        row = torch.tensor([generated, max_tokens, 1 if ignore_eos else 0, 0], dtype=torch.int32)
+        self.slot_state[self.cache.slot(request_id)].copy_(row, non_blocking=True)
+
     def close(self, request_id: Any) -> None:
         self.cache.close(request_id)
 
@@ -353,8 +364,10 @@ class ModelRunner:
         kv_len = pos0 + q_lens
         slots = np.fromiter((self.cache.slot(e.request_id) for e in entries), dtype=np.int64, count=B)
         rows: List[int] = []
+        row_slots: List[int] = []
         for i, e in enumerate(entries):
             rows.extend(int(cu_q[i]) + int(w) for w in e.want)
+            row_slots.extend([int(slots[i])] * len(e.want))
 
         sections: List[np.ndarray] = [token_ids, positions, cu_q, kv_len, slots,
                                       np.asarray(rows, dtype=np.int64)]
@@ -373,6 +386,7 @@ class ModelRunner:
             sections += [table.reshape(-1), slot_of_token]
         decode_list = np.flatnonzero(q_lens == 1)
         sections.append(decode_list)
+        sections.append(np.asarray(row_slots, dtype=np.int64))
         for r, skip_decode in [(r, False) for r in self.tile_rows] + [(r, True) for r in self.prefill_tile_rows]:
             n_tiles = (q_lens + r - 1) // r
             if skip_decode:
@@ -402,6 +416,7 @@ class ModelRunner:
             table = next(it).view(B, max_blocks)
             groups.append(GroupStep(table, next(it)))
         decode_entries = next(it)
+        self.last_want_slots = next(it)
         tiles = {r: (next(it), next(it)) for r in self.tile_rows}
         prefill_tiles = {r: (next(it), next(it)) for r in self.prefill_tile_rows}
         host_entries = [HostEntry(e.request_id, int(slots[i]), int(q_lens[i]), int(pos0[i]))
@@ -471,10 +486,14 @@ class ModelRunner:
         _lib.launch_count += g.kernels_per_replay
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if not wanted:
+            self.last_want_slots = None
             return None
         if len(wanted) == len(entries):
+            self.last_want_slots = g.step.state_slots[: len(entries)]
             return g.logits[: len(entries)]
-        return g.logits[torch.tensor(wanted, device=self.device)]
+        idx = torch.tensor(wanted, device=self.device)
+        self.last_want_slots = g.step.state_slots[idx]
+        return g.logits[idx]
 
     def check_kernel_errors(self) -> None:
         """Raise if a kernel recorded a fault it survived (a bounded wait that ran out).

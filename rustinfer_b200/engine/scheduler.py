@@ -35,6 +35,7 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
 WAITING, PREFILL, DECODE, FINISHED = "waiting", "prefill", "decode", "finished"
+DRAINING = "draining"     # its last token is chosen but not yet delivered to the host: nothing more to run
 
 
 @dataclass
@@ -49,6 +50,7 @@ class Request:
     admitted_at: int = -1                # admission counter, for the choice of a victim
     preemptions: int = 0
     finish_reason: Optional[str] = None
+    undelivered: int = 0                 # tokens chosen on the device that the host has not read yet
 
     @property
     def sequence(self) -> List[int]:
@@ -231,7 +233,7 @@ class Scheduler:
             budget -= n
 
         # 4. nothing can move although requests are under way: the youngest gives way
-        if not plan.entries and self.running:
+        if not plan.entries and any(r.state in (PREFILL, DECODE) for r in self.running):
             if len(self.running) == 1:
                 self._fail(self.running[0], "kv_pool_exhausted")
             else:
@@ -253,16 +255,40 @@ class Scheduler:
         """`sampled[i]` is the token chosen for the i-th entry of the plan that samples.
         The step function has already committed the tokens to the cache.  Returns the
         requests that finished with this step."""
-        done: List[Request] = []
-        it = iter(sampled)
+        self.advance(plan)
+        return self.deliver(plan, sampled)
+
+    def advance(self, plan: StepPlan) -> None:
+        """The step has been launched: count its tokens as computed.  What it chose is not
+        known yet (`deliver` brings it), so the next step can be planned, and launched with
+        the chosen tokens fed on the device, before the host has read them.  A request whose
+        chosen token is its last by length runs no further (`DRAINING`)."""
         for e in plan.entries:
             req = e.request
             req.computed += e.count
             if not e.samples:
                 continue
-            tok = int(next(it))
-            req.output.append(tok)
+            req.undelivered += 1
             req.state = DECODE
+            made = len(req.output) + req.undelivered
+            if made >= req.params.max_tokens or len(req.prompt) + made >= self.max_model_len:
+                req.state = DRAINING
+
+    def deliver(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """The tokens of a launched step have reached the host.  A request that already
+        finished (a stop token in an earlier delivery, while this step was in flight) ignores
+        what this step chose for it."""
+        done: List[Request] = []
+        it = iter(sampled)
+        for e in plan.entries:
+            if not e.samples:
+                continue
+            req = e.request
+            tok = int(next(it))
+            if req.state == FINISHED:
+                continue
+            req.undelivered -= 1
+            req.output.append(tok)
             # crates/infer-worker/src/application/runtime/mod.rs:1198-1214: eos unless ignored,
             # or the count of generated tokens reaches max_tokens (the first token counts)
             if tok in self.eos and not req.params.ignore_eos:
@@ -272,8 +298,12 @@ class Scheduler:
             elif len(req.prompt) + len(req.output) >= self.max_model_len:
                 req.finish_reason = "length"
             if req.finish_reason:
-                self.cache.close(req.request_id)
-                self.running.remove(req)
+                if self.cache.is_open(req.request_id):
+                    self.cache.close(req.request_id)
+                if req in self.running:
+                    self.running.remove(req)
+                elif req in self.waiting:              # it gave way while its last token was in flight
+                    self.waiting.remove(req)
                 req.state = FINISHED
                 self.finished.append(req)
                 done.append(req)

@@ -321,6 +321,25 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, state: Optional[torch.Tensor
                              stream_ptr()), "argmax")
 
 
+def decode_feedback(sampled: torch.Tensor, state_slots: torch.Tensor, slot_state: torch.Tensor,
+                    eos_ids: Optional[torch.Tensor], result: torch.Tensor,
+                    token_feed: Optional[torch.Tensor]) -> None:
+    """Per row of a decode step: count the chosen token in slot_state[slot] = {generated,
+    max_tokens, ignore_eos, last_token}, write result = [tokens | stop flags] (int32
+    [2 * rows]) and copy the token to `token_feed`, the next step's input ids."""
+    require_cuda(sampled, state_slots, slot_state, eos_ids, result, token_feed)
+    rows = sampled.numel()
+    for t, n in ((sampled, "sampled"), (state_slots, "state_slots"), (slot_state, "slot_state"),
+                 (eos_ids, "eos_ids"), (result, "result"), (token_feed, "token_feed")):
+        _i32(t, n)
+    if state_slots.numel() < rows or result.numel() < 2 * rows or slot_state.dim() != 2 or slot_state.shape[1] != 4 \
+            or not slot_state.is_contiguous() or (token_feed is not None and token_feed.numel() < rows):
+        raise KernelError("decode_feedback: sizes")
+    check(L.core().ri_decode_feedback(_p(sampled), _p(state_slots), rows, _p(slot_state), _p(eos_ids),
+                                      0 if eos_ids is None else eos_ids.numel(), _p(result), _p(token_feed),
+                                      stream_ptr()), "decode_feedback")
+
+
 def sample(logits: torch.Tensor, scratch: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, min_p: torch.Tensor, draw: torch.Tensor, out: torch.Tensor) -> None:
     require_cuda(logits, scratch, temperature, top_k, top_p, min_p, draw, out)

@@ -56,11 +56,17 @@ class Sampler:
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                positions: Sequence[int]) -> List[int]:
         """logits fp32 [R, vocab]; row i is drawn with params[i], seeds[i] at positions[i]."""
+        return self.sample_device(logits, params, seeds, positions).tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
+                      positions: Sequence[int]) -> torch.Tensor:
+        """As `sample`, but the chosen ids stay on the device (int32 [R], valid until the
+        next call)."""
         R = logits.shape[0]
         if R > self.max_rows:
             raise ValueError(f"{R} rows exceed the sampler's {self.max_rows}")
         if all(p.is_greedy() for p in params):
-            return self.argmax_device(logits).tolist()
+            return self.argmax_device(logits)
         if self._scratch is None:
             self._scratch = torch.empty(K.sample_scratch_elems(self.max_rows, self.vocab),
                                         dtype=torch.int64, device=self.device)
@@ -73,4 +79,4 @@ class Sampler:
         out = self._out[:R]
         K.sample(logits, self._scratch, f[:, 0].contiguous(), host_k.to(self.device), f[:, 1].contiguous(),
                  f[:, 2].contiguous(), host_u.to(self.device), out)
-        return out.tolist()
+        return out

@@ -258,6 +258,7 @@ def test_greedy_generation_through_the_entry_point(models, name, dtype):
                 seq.append(t)
     assert eng.runner.cache.free_pages() == {0: 20}
     assert eng.stats.generated_tokens == 64
+    assert eng.stats.stop_flag_mismatches == 0                # the device's stop check agrees with the host's
 
 
 def test_seeded_sampling_does_not_depend_on_the_batch(models):
@@ -347,3 +348,37 @@ def test_decode_graphs_equal_eager_steps(models, dtype):
     toks = torch.tensor(seqs[0][6:12], dtype=torch.int32, device="cuda:0")
     outs = [graph.step([StepEntry(0, [0], [0])], device_tokens=toks[k: k + 1]) .clone() for k in range(6)]
     assert rel_err(torch.cat(outs), plain.logits(seqs[0])[6:12]) <= TOL[dtype]
+
+
+def test_stop_ids_end_generation_where_the_plain_model_says(models, tmp_path):
+    """Stop ids from config.json end a request at the first of them (unless ignored); the
+    device-side stop check and the host agree on every token, also while steps are chained."""
+    import json
+    import shutil
+    import plain_llama
+    from rustinfer_b200.engine.engine import Engine
+    from rustinfer_b200.sampling.params import SamplingParams
+    folder, plain = models["A"]
+    V = TINY["A"]["vocab_size"]
+    prompts = [random_ids(n, V, 300 + n) for n in (4, 9, 15, 2, 11, 6)]
+    free_run = [plain_llama.greedy_generate(plain.cfg, plain.w, p, 24) for p in prompts]
+    # stop ids: for each sequence, a token from the middle of its free-running continuation
+    eos = sorted({seq[8 + i] for i, seq in enumerate(free_run)})
+    stop_folder = str(tmp_path / "with_eos")
+    shutil.copytree(folder, stop_folder)
+    cfg = dict(plain.cfg, eos_token_id=eos)
+    with open(os.path.join(stop_folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    eng = Engine(stop_folder, dtype="float32", max_batch_tokens=64, max_batch_seqs=4, max_model_len=64,
+                 paged_block_size=8, num_blocks=40)
+    res = eng.generate(prompts, SamplingParams(max_tokens=24))
+    for seq, out in zip(free_run, res):
+        cut = next((i for i, t in enumerate(seq) if t in eos), None)
+        want = seq if cut is None else seq[: cut + 1]
+        assert out.tokens == want
+        assert out.finish_reason == ("length" if cut is None else "stop")
+    assert any(o.finish_reason == "stop" for o in res)
+    assert eng.stats.stop_flag_mismatches == 0
+    ignored = eng.generate(prompts[:2], SamplingParams(max_tokens=24, ignore_eos=True))
+    assert [o.tokens for o in ignored] == free_run[:2] and eng.stats.stop_flag_mismatches == 0
+    assert eng.runner.cache.free_pages() == {0: 40}
