@@ -196,7 +196,7 @@ def decode_e2e(engine, batch, steps, warmup, vocab, seed):
     for rid in list(engine._requests):
         engine.abort(rid)
     assert got == batch * (steps - 1), (got, batch, steps)
-    return ms, h2d, batch * 4, (w0, w1)
+    return ms, h2d, batch * 8, (w0, w1)       # read back per step: a token id and a stop flag per request
 
 
 def prefill_timed(engine, vocab, tokens, repeats=3):
