@@ -38,7 +38,19 @@ constexpr int THREADS = 128;
 constexpr int MT = 64;                 // rows per prefill CTA
 // K/V tiles a decode CTA keeps in flight: decode is a pure stream of the cache, and what
 // bounds it is how many bytes every SM has on the way
-constexpr int DSTAGES = HD <= 64 ? 4 : (HD <= 128 ? 3 : 2);
+// Measured on B200 (32/8 heads of 64, 4,096 keys; us for batch 8 / batch 64, best split each):
+// 4 warps x 2 stages 20.6 / 107, 4 x 4 22.0 / 127, 8 x 2 22.8 / 114, 6 x 2 24.2 / 129.  More CTAs
+// per SM (5 at 39 KB each) beat deeper rings.
+#ifndef RI_DEC_WARPS
+#define RI_DEC_WARPS 4
+#endif
+#ifndef RI_DEC_STAGES
+#define RI_DEC_STAGES 2
+#endif
+constexpr int DWARPS = RI_DEC_WARPS;                 // warps of a decode CTA, 16 keys of every tile each
+constexpr int DTHREADS = 32 * DWARPS;
+constexpr int DKT = 16 * DWARPS;                     // keys per decode tile
+constexpr int DSTAGES = RI_DEC_STAGES;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -71,12 +83,13 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // K and V rows of keys k0 .. k0+KT-1 of one kv head into smem; keys outside [k_lo, k_hi)
 // are zero-filled and their pages are never looked up.
+template <int TILE_KEYS, int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(bf16* Ks, bf16* Vs, const bf16* __restrict__ cache,
                                              const int* __restrict__ bt, int k0, int k_lo, int k_hi,
                                              int Hkv, int kvh, int page_size) {
     const size_t head_step = (size_t)page_size * HD;
     const int shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;   // power of two: no division
-    for (int c = threadIdx.x; c < KT * CH; c += THREADS) {
+    for (int c = threadIdx.x; c < TILE_KEYS * CH; c += NTHREADS) {
         const int kk = c / CH, ch = c - kk * CH;
         const int key = k0 + kk;
         const bool ok = key >= k_lo && key < k_hi;
@@ -136,7 +149,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
     const int t_begin = lo_tile / KT, t_end = p_last / KT + 1;
     const int* bt = block_table + (size_t)b * table_stride;
 
-    load_kv_tile(KVs, KVs + KT * ROW, cache, bt, t_begin * KT, lo_tile, p_last + 1, Hkv, kvh, page_size);
+    load_kv_tile<KT, THREADS>(KVs, KVs + KT * ROW, cache, bt, t_begin * KT, lo_tile, p_last + 1, Hkv, kvh, page_size);
     cp_async_commit();
     __syncthreads();                                          // Qs is written
 
@@ -169,7 +182,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
         bf16* Vs = Ks + KT * ROW;
         if (t + 1 < t_end) {
             bf16* Kn = KVs + (buf ^ 1) * 2 * KT * ROW;
-            load_kv_tile(Kn, Kn + KT * ROW, cache, bt, (t + 1) * KT, lo_tile, p_last + 1, Hkv, kvh, page_size);
+            load_kv_tile<KT, THREADS>(Kn, Kn + KT * ROW, cache, bt, (t + 1) * KT, lo_tile, p_last + 1, Hkv, kvh, page_size);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -273,7 +286,7 @@ prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
 // ========================================================================== decode
 // grid (kv heads * head chunks, splits, decode entries).  part_o [entries][Hq][splits][HD]
 // fp32 and part_lse [entries][Hq][splits] (base-2 log-sum-exp) are written when splits > 1.
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(DTHREADS)
 decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
               const bf16* __restrict__ cache, const int* __restrict__ block_table, int table_stride,
               const int* __restrict__ cu_q, const int* __restrict__ kv_len,
@@ -284,7 +297,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);            // [16][ROW]
-    bf16* KVs = Qs + 16 * ROW;                               // [DSTAGES][K|V][KT][ROW]
+    bf16* KVs = Qs + 16 * ROW;                               // [DSTAGES][K|V][DKT][ROW]
 
     const int slot = blockIdx.z;
     const int b = entry_list ? entry_list[slot] : slot;
@@ -297,7 +310,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     const int tok = cu_q[b + 1] - 1;                          // the entry's (last) token row
     const int kvl = kv_len[b];
     const int lo = window > 0 ? max(0, kvl - window) : 0;
-    const int t_first = lo / KT, t_count = (kvl + KT - 1) / KT - t_first;
+    const int t_first = lo / DKT, t_count = (kvl + DKT - 1) / DKT - t_first;
     const int per = (t_count + splits - 1) / splits;
     const int t_begin = t_first + split * per, t_end = min(t_begin + per, t_first + t_count);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -307,12 +320,12 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
 #pragma unroll
     for (int i = 0; i < DSTAGES - 1; ++i) {
         if (t_begin + i < t_end) {
-            bf16* Kb = KVs + i * 2 * KT * ROW;
-            load_kv_tile(Kb, Kb + KT * ROW, cache, bt, (t_begin + i) * KT, lo, kvl, Hkv, kvh, page_size);
+            bf16* Kb = KVs + i * 2 * DKT * ROW;
+            load_kv_tile<DKT, DTHREADS>(Kb, Kb + DKT * ROW, cache, bt, (t_begin + i) * DKT, lo, kvl, Hkv, kvh, page_size);
         }
         cp_async_commit();
     }
-    for (int c = tid; c < 16 * CH; c += THREADS) {
+    for (int c = tid; c < 16 * CH; c += DTHREADS) {
         const int r = c / CH, ch = c - r * CH;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (r < nheads)
@@ -333,19 +346,19 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
 
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) % DSTAGES;
-        bf16* Ks = KVs + buf * 2 * KT * ROW;
-        bf16* Vs = Ks + KT * ROW;
+        bf16* Ks = KVs + buf * 2 * DKT * ROW;
+        bf16* Vs = Ks + DKT * ROW;
         cp_async_wait<DSTAGES - 2>();                         // tile t has landed (this thread's part)
         __syncthreads();                                      // ... everyone's part; and tile t-1 is consumed
         {
             const int tn = t + DSTAGES - 1;                   // refill the buffer tile t-1 used
             if (tn < t_end) {
-                bf16* Kn = KVs + ((tn - t_begin) % DSTAGES) * 2 * KT * ROW;
-                load_kv_tile(Kn, Kn + KT * ROW, cache, bt, tn * KT, lo, kvl, Hkv, kvh, page_size);
+                bf16* Kn = KVs + ((tn - t_begin) % DSTAGES) * 2 * DKT * ROW;
+                load_kv_tile<DKT, DTHREADS>(Kn, Kn + DKT * ROW, cache, bt, tn * DKT, lo, kvl, Hkv, kvh, page_size);
             }
             cp_async_commit();
         }
-        if (t * KT + kw0 < kvl) {                             // the warp's keys are not all past the end
+        if (t * DKT + kw0 < kvl) {                             // the warp's keys are not all past the end
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
@@ -354,7 +367,7 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
                 mma_bf16(s[0], qf[ks], kf[0], kf[1]);
                 mma_bf16(s[1], qf[ks], kf[2], kf[3]);
             }
-            const int key0 = t * KT + kw0 + (lane & 3) * 2;
+            const int key0 = t * DKT + kw0 + (lane & 3) * 2;
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int n = 0; n < 2; ++n)
@@ -404,10 +417,10 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     cp_async_wait<0>();
     __syncthreads();
 
-    // merge the four warps' states through shared memory (the K/V buffers are free now)
-    float* Os = reinterpret_cast<float*>(KVs);               // [4][16][HD]
-    float* Ms = Os + 4 * 16 * HD;                            // [4][16]
-    float* Ls = Ms + 64;                                     // [4][16]
+    // merge the warps' states through shared memory (the K/V buffers are free now)
+    float* Os = reinterpret_cast<float*>(KVs);               // [DWARPS][16][HD]
+    float* Ms = Os + DWARPS * 16 * HD;                       // [DWARPS][16]
+    float* Ls = Ms + DWARPS * 16;                            // [DWARPS][16]
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
@@ -425,15 +438,15 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < nheads * HD; idx += THREADS) {
+    for (int idx = tid; idx < nheads * HD; idx += DTHREADS) {
         const int r = idx / HD, d = idx - r * HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, Ms[w * 16 + r]);
+        for (int w = 0; w < DWARPS; ++w) M = fmaxf(M, Ms[w * 16 + r]);
         float L = 0.f, O = 0.f;
         if (M != -INFINITY) {
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
+            for (int w = 0; w < DWARPS; ++w) {
                 const float f = exp2f(Ms[w * 16 + r] - M);
                 L += Ls[w * 16 + r] * f;
                 O += Os[((size_t)w * 16 + r) * HD + d] * f;
@@ -478,8 +491,8 @@ __global__ void combine_kernel(const float* __restrict__ part_o, const float* __
 }
 
 constexpr size_t PREFILL_SMEM = ((size_t)MT * ROW + 4 * (size_t)KT * ROW) * sizeof(bf16);
-constexpr size_t DECODE_SMEM_KV = 2 * (size_t)DSTAGES * KT * ROW * sizeof(bf16);
-constexpr size_t DECODE_SMEM_MERGE = (4 * 16 * (size_t)HD + 128) * sizeof(float);
+constexpr size_t DECODE_SMEM_KV = 2 * (size_t)DSTAGES * DKT * ROW * sizeof(bf16);
+constexpr size_t DECODE_SMEM_MERGE = (DWARPS * 16 * (size_t)HD + 2 * DWARPS * 16) * sizeof(float);
 constexpr size_t DECODE_SMEM = 16 * (size_t)ROW * sizeof(bf16) +
                                (DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE);
 
@@ -497,6 +510,13 @@ int configure() {
 }  // namespace
 
 RI_API int ri_attention_mma_head_dim() { return HD; }
+RI_API int ri_attention_decode_tile_keys() { return DKT; }
+// CTAs of the decode kernel that fit one SM (by shared memory), for the choice of key ranges
+RI_API int ri_attention_decode_ctas_per_sm() {
+    const int by_smem = (int)((227 * 1024) / (DECODE_SMEM + 1024));
+    const int by_threads = 2048 / DTHREADS;
+    return by_smem < by_threads ? (by_smem < 1 ? 1 : by_smem) : by_threads;
+}
 
 // Tokens per prefill tile for a model with `group` q heads per kv head: 64 rows hold
 // 64 / min(group, 64) tokens of min(group, 64) heads each.
@@ -537,7 +557,7 @@ RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int 
     const int G = Hq / Hkv, Gc = G < 16 ? G : 16, chunks = (G + Gc - 1) / Gc;
     dim3 grid(Hkv * chunks, splits, n_entries);
     cudaStream_t s = (cudaStream_t)stream;
-    RI_CHECKED(ri_launch(decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, s, 
+    RI_CHECKED(ri_launch(decode_kernel, dim3(grid), dim3(DTHREADS), DECODE_SMEM, s, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
         cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,
         splits, part_o, part_lse));
@@ -621,7 +641,7 @@ int ri_attention_decode_bf16_static(const void* q, int q_stride, void* out, int 
     const int G = Hq / Hkv, Gc = G < 16 ? G : 16, chunks = (G + Gc - 1) / Gc;
     dim3 grid(Hkv * chunks, splits, n_entries);
     cudaStream_t s = (cudaStream_t)stream;
-    RI_CHECKED(ri_launch(decode_kernel, dim3(grid), dim3(THREADS), DECODE_SMEM, s, 
+    RI_CHECKED(ri_launch(decode_kernel, dim3(grid), dim3(DTHREADS), DECODE_SMEM, s, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
         cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,
         splits, part_o, part_lse));

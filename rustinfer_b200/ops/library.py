@@ -107,7 +107,16 @@ def attention_mma(head_dim: int) -> ctypes.CDLL:
     if head_dim % 16 != 0 or not 16 <= head_dim <= MMA_MAX_HEAD_DIM:
         raise KernelError(f"the tensor-core attention kernels take head sizes that are multiples of 16 "
                           f"up to {MMA_MAX_HEAD_DIM}, got {head_dim}")
-    return _load(f"ri_attention_mma_hd{head_dim}", ["attention_mma.cu"], [f"RI_HEAD_DIM={head_dim}"])
+    name, defines = f"ri_attention_mma_hd{head_dim}", [f"RI_HEAD_DIM={head_dim}"]
+    tune = os.environ.get("RUSTINFER_B200_DECODE_TUNE")       # "warps,stages": for tuning runs only
+    if tune:
+        w, st = tune.split(",")
+        name += f"_w{w}s{st}"
+        defines += [f"RI_DEC_WARPS={int(w)}", f"RI_DEC_STAGES={int(st)}"]
+    lib = _load(name, ["attention_mma.cu"], defines)
+    lib.ri_attention_decode_ctas_per_sm.restype = _I
+    lib.ri_attention_decode_tile_keys.restype = _I
+    return lib
 
 
 def build_all(head_dims) -> None:

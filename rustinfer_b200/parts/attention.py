@@ -73,6 +73,9 @@ class GQAAttention(Mixer):
                 ctx.shared[key] = (torch.empty(no, dtype=torch.float32, device=ctx.device),
                                    torch.empty(nl, dtype=torch.float32, device=ctx.device))
             self.part_o, self.part_lse = ctx.shared[key]
+            lib = L.attention_mma(self.hd)
+            self.decode_ctas_per_sm = int(lib.ri_attention_decode_ctas_per_sm())
+            self.decode_tile_keys = int(lib.ri_attention_decode_tile_keys())
         else:
             self.attention_tile_rows = (16,)
             self.prefill_tile_rows = ()
@@ -133,17 +136,17 @@ class GQAAttention(Mixer):
         return self._project_out(out, residual)
 
     def _splits(self, n_decode: int, max_kv_len: int) -> int:
-        """Ranges each decoding request's keys are cut into.  About three CTAs sit on an SM
-        (each keeps several K/V tiles in flight).  A grid that fits one wave is best filled
-        as far as it goes; a grid of several waves pays for every wave's start and end, so it
-        is scored by how full its last wave is, at a discount.  Measured on B200, batch 8 at
-        4,096 keys: 6 ranges (384 CTAs, one wave) 21.9 us, 7 ranges (a second wave of four
-        CTAs) 27.1 us, 13 ranges 25.6 us.  Never more ranges than 64-key tiles."""
+        """Ranges each decoding request's keys are cut into.  A few CTAs sit on an SM (the
+        kernel says how many).  A grid that fits one wave is best filled as far as it goes; a
+        grid of several waves pays for every wave's start and end, so it is scored by how
+        full its last wave is, at a discount.  Measured on B200 at 4,096 keys with 5 CTAs per
+        SM: batch 8, 11 ranges (704 CTAs, one wave) 20.6 us, 13 ranges (a second wave) 26.1 us;
+        batch 64, 4 ranges 107 us, 1 range 138 us.  Never more ranges than tiles of keys."""
         chunks = (self.Hq // self.Hkv + 15) // 16
         ctas = n_decode * self.Hkv * chunks
         span = min(max_kv_len, self.window) if self.window else max_kv_len
-        tiles = max(1, (span + 63) // 64)
-        slots = 3 * self.ctx.num_sms
+        tiles = max(1, -(-span // self.decode_tile_keys))
+        slots = self.decode_ctas_per_sm * self.ctx.num_sms
         best, best_score = 1, -1.0
         for s in range(1, min(tiles, self.MAX_SPLITS) + 1):
             waves = ctas * s / slots
