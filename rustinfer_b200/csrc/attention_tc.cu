@@ -1,0 +1,530 @@
+// Paged causal GQA attention for prompt portions on the 5th-generation tensor cores:
+// S = Q K^T and O_tile = P V are tcgen05.mma instructions with fp32 accumulators in tensor
+// memory; K and V tiles are fetched page by page with TMA straight from the paged cache
+// (a box per page and kv head); the softmax runs in registers, one thread per query row.
+// Compiled for one RI_HEAD_DIM (64 or 128).
+//
+// RustInfer's ragged attention is an mma.sync kernel with one CTA per q head that gathers
+// keys token by token (crates/infer-backend-cuda/src/kernels/flash_attn_gqa/
+// flash_attn_paged_prefill.cu:316-520) or, on Hopper, vendored FlashAttention-3 (wgmma);
+// neither exists for sm_100.  What is computed is the same: row (token, q head) sees keys
+// 0..position (or a window), scores scaled by 1/sqrt(head_dim) in base 2, probabilities
+// rounded to bf16 for P V, fp32 sums.
+//
+// One CTA = 128 rows x one kv head; a row is (query token, q head of the kv head's group),
+// so the group's heads share every K/V tile.  192 threads:
+//   warp 0      TMA producer (one thread): K and V boxes of each 64-key tile, 3 stages each
+//   warp 1      tensor memory allocation; one thread issues the MMAs, S of tile j+1 before
+//               P V of tile j, so the tensor core computes scores while the softmax of the
+//               tile before is still running
+//   warps 2-5   softmax: thread = row; tcgen05.ld of the row's 64 scores, online softmax,
+//               P (bf16) written to swizzled shared memory as the A operand of P V.  The
+//               output accumulates in tensor memory across tiles; it is rescaled (load,
+//               multiply, store) only when a row's maximum has grown by more than 2^8 since
+//               the reference it was scaled to, which after the first tiles is rare
+// Every wait on an mbarrier is bounded; a time-out leaves a code in *error and the kernel
+// winds down (tensor memory freed, copies in flight drained).
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#ifndef RI_HEAD_DIM
+#error "compile with -DRI_HEAD_DIM=<head size>"
+#endif
+
+namespace {
+constexpr int HD = RI_HEAD_DIM;
+static_assert(HD == 64 || HD == 128, "tcgen05 attention: head size 64 or 128");
+constexpr int BM = 128;                   // rows per CTA (MMA M)
+constexpr int BN = 64;                    // keys per tile
+constexpr int KB = HD / 64;               // 64-wide column blocks of a head (one 128-byte swizzle row each)
+constexpr int NS = 2;                     // stages of K and of V
+constexpr int THREADS = 192;
+constexpr unsigned SPIN_LIMIT = 1u << 20;
+constexpr int TMEM_COLS = HD == 64 ? 128 : 256;   // S: 64 columns, O: HD columns
+constexpr int COL_S = 0, COL_O = BN;
+constexpr float RESCALE_STEP = 8.0f;              // log2 of the growth of a row's maximum that forces a rescale
+
+constexpr int Q_BYTES = BM * 128 * KB;            // [KB][128 rows][128 B]
+constexpr int KV_STAGE = BN * 128 * KB;           // [KB][64 keys][128 B]
+constexpr int P_BYTES = BM * 128;                 // [128 rows][64 keys] bf16
+constexpr int OFF_Q = 0, OFF_K = OFF_Q + Q_BYTES, OFF_V = OFF_K + NS * KV_STAGE, OFF_P = OFF_V + NS * KV_STAGE;
+constexpr int OFF_BAR = OFF_P + P_BYTES;
+constexpr size_t SMEM = (size_t)OFF_BAR + 512 + 1024 /*alignment*/;
+
+enum { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* error, int code) {
+    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 1024) __nanosleep(64);
+    }
+    atomicExch(error, code);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory descriptors, 128-byte swizzle, 8-row groups 1024 bytes apart.
+//  K-major (rows of 64 contraction elements): Q, K and P.
+__device__ __forceinline__ uint64_t desc_kmajor(unsigned addr) {
+    return (uint64_t)((addr & 0x3ffff) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+//  MN-major (rows are keys = the contraction, 64 head dims contiguous): V as loaded from the
+//  cache.  Leading offset: between 64-dim column blocks; stride offset: between 8-key groups.
+__device__ __forceinline__ uint64_t desc_mnmajor(unsigned addr) {
+    return (uint64_t)((addr & 0x3ffff) >> 4) | ((uint64_t)((BN * 128) >> 4) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void mma_ss(unsigned tmem_d, uint64_t a, uint64_t b, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 16 consecutive fp32 columns of this thread's lane into r[0..15] (complete after tmem_ld_wait)
+__device__ __forceinline__ void tmem_ld16_issue(unsigned addr, float* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+                   "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15])
+                 : "r"(addr));
+}
+// 64 consecutive fp32 columns in one instruction
+__device__ __forceinline__ void tmem_ld64_issue(unsigned addr, float* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+        "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+        : "=f"(r[0]), "=f"(r[1]), "=f"(r[2]), "=f"(r[3]), "=f"(r[4]), "=f"(r[5]), "=f"(r[6]), "=f"(r[7]),
+          "=f"(r[8]), "=f"(r[9]), "=f"(r[10]), "=f"(r[11]), "=f"(r[12]), "=f"(r[13]), "=f"(r[14]), "=f"(r[15]),
+          "=f"(r[16]), "=f"(r[17]), "=f"(r[18]), "=f"(r[19]), "=f"(r[20]), "=f"(r[21]), "=f"(r[22]), "=f"(r[23]),
+          "=f"(r[24]), "=f"(r[25]), "=f"(r[26]), "=f"(r[27]), "=f"(r[28]), "=f"(r[29]), "=f"(r[30]), "=f"(r[31]),
+          "=f"(r[32]), "=f"(r[33]), "=f"(r[34]), "=f"(r[35]), "=f"(r[36]), "=f"(r[37]), "=f"(r[38]), "=f"(r[39]),
+          "=f"(r[40]), "=f"(r[41]), "=f"(r[42]), "=f"(r[43]), "=f"(r[44]), "=f"(r[45]), "=f"(r[46]), "=f"(r[47]),
+          "=f"(r[48]), "=f"(r[49]), "=f"(r[50]), "=f"(r[51]), "=f"(r[52]), "=f"(r[53]), "=f"(r[54]), "=f"(r[55]),
+          "=f"(r[56]), "=f"(r[57]), "=f"(r[58]), "=f"(r[59]), "=f"(r[60]), "=f"(r[61]), "=f"(r[62]), "=f"(r[63])
+        : "r"(addr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(unsigned addr, const float* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(addr), "f"(r[0]), "f"(r[1]), "f"(r[2]), "f"(r[3]), "f"(r[4]), "f"(r[5]), "f"(r[6]), "f"(r[7]),
+                   "f"(r[8]), "f"(r[9]), "f"(r[10]), "f"(r[11]), "f"(r[12]), "f"(r[13]), "f"(r[14]), "f"(r[15])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 2^x on the special-function unit, one instruction (inputs here are <= 0 or -inf)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct Params {
+    const bf16* q; int q_stride;
+    bf16* out; int out_stride;
+    const int* block_table; int table_stride;
+    const int* cu_q; const int* kv_len; const int* tile_entry; const int* tile_tok0;
+    int Hq, Hkv, G, tpt, page_size, box_rows;
+    float scale_log2; int window;
+    int* error;
+};
+
+// three CTAs per SM for heads of 64, two for 128 (tensor memory, shared memory and registers
+// allow it): the other CTAs' softmax fills the issue slots one leaves while it waits on its chain
+__global__ void __launch_bounds__(THREADS, HD == 64 ? 3 : 2)
+attention_tc_kernel(const __grid_constant__ CUtensorMap cache_map, const Params p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BAR);
+    uint64_t* k_full = bars;              // [NS]
+    uint64_t* k_empty = k_full + NS;      // [NS]
+    uint64_t* v_full = k_empty + NS;      // [NS]
+    uint64_t* v_empty = v_full + NS;      // [NS]
+    uint64_t* s_full = v_empty + NS;      // scores of a tile are in tensor memory
+    uint64_t* s_empty = s_full + 1;       // ... and have been read into registers
+    uint64_t* p_full = s_empty + 1;       // probabilities of a tile are in shared memory
+    uint64_t* p_empty = p_full + 1;       // ... and P V has read them
+    uint64_t* o_done = p_empty + 1;       // P V of a tile has been added to the output
+    uint64_t* q_ready = o_done + 1;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(q_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // CTAs start in the order x fastest: all kv heads of the last tile first, the first tile
+    // last.  In a causal prompt the late tiles see the most keys, so the long CTAs start
+    // early and the short ones fill the end of the last wave.
+    const int tile = gridDim.y - 1 - blockIdx.y;
+    const int b = p.tile_entry[tile];
+    const int tok0 = p.tile_tok0[tile];
+    const int g = blockIdx.x;                                  // kv head
+    const int q_begin = b >= 0 ? p.cu_q[b] : 0, q_len = b >= 0 ? p.cu_q[b + 1] - q_begin : 0;
+    const int kvl = b >= 0 ? p.kv_len[b] : 0;
+    const int pos0 = kvl - q_len;
+    const int ntok = min(p.tpt, q_len - tok0);
+    const int p_first = pos0 + tok0, p_last = p_first + ntok - 1;
+    const int lo_tile = p.window > 0 ? max(0, p_first - p.window + 1) : 0;
+    const int t_begin = lo_tile / BN, t_end = p_last / BN + 1;
+    const int n_tiles = (b >= 0 && ntok > 0) ? t_end - t_begin : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+        }
+        mbar_init(s_full, 1); mbar_init(s_empty, 4);
+        mbar_init(p_full, 4); mbar_init(p_empty, 1);
+        mbar_init(o_done, 1);
+        mbar_init(q_ready, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    pdl_trigger();
+
+    if (warp == 0 && lane == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        pdl_wait();                                            // the cache was written by the kernel before
+        const int* bt = p.block_table + (size_t)b * p.table_stride;
+        const int boxes = BN / p.box_rows;
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int s = j % NS, u = j / NS;
+            const int key0 = (t_begin + j) * BN;
+            for (int kv = 0; kv < 2 && ok; ++kv) {
+                uint64_t* full = kv ? &v_full[s] : &k_full[s];
+                uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
+                if (u > 0 && !mbar_wait(empty, (u - 1) & 1, p.error, ERR_PRODUCER)) { ok = false; break; }
+                unsigned char* dst = sm + (kv ? OFF_V : OFF_K) + s * KV_STAGE;
+                mbar_expect_tx(full, KV_STAGE);
+                for (int c = 0; c < boxes; ++c) {
+                    const int key = key0 + c * p.box_rows;
+                    // pages past the request's last one are never allocated: read its first page
+                    // instead (those keys are masked, and their V rows are zeroed before use)
+                    const int blk = key < kvl ? key / p.page_size : 0;
+                    const int page = bt[blk];
+                    const int row = ((page * 2 + kv) * p.Hkv + g) * p.page_size + (key < kvl ? key % p.page_size : 0);
+                    for (int kb = 0; kb < KB; ++kb)
+                        tma_load_2d(dst + kb * (BN * 128) + c * p.box_rows * 128, &cache_map, full, kb * 64, row);
+                }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // -------------------------------------------------------------------- MMA issuer
+        // D fp32, A and B bf16; S: both K-major, N = 64; P V: B is MN-major, N = HD
+        const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+        const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(HD >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+        const unsigned q_addr = smem_u32(sm + OFF_Q);
+        bool ok = n_tiles > 0 && mbar_wait(q_ready, 0, p.error, ERR_MMA);
+        auto issue_s = [&](int j) -> bool {
+            const int s = j % NS, u = j / NS;
+            if (!mbar_wait(&k_full[s], u & 1, p.error, ERR_MMA)) return false;
+            if (!mbar_wait(s_empty, (j & 1) ^ 1, p.error, ERR_MMA)) return false;   // scores of tile j-1 were read
+            tc_fence_after();
+            const unsigned k_addr = smem_u32(sm + OFF_K + s * KV_STAGE);
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+                    mma_ss(tmem_base + COL_S, desc_kmajor(q_addr + kb * (BM * 128) + k * 32),
+                           desc_kmajor(k_addr + kb * (BN * 128) + k * 32), idesc_s, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_commit(&k_empty[s]);
+            tc_commit(s_full);
+            return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            if (j + 1 < n_tiles) ok = issue_s(j + 1);
+            if (!ok) break;
+            const int s = j % NS, u = j / NS;
+            if (!mbar_wait(p_full, j & 1, p.error, ERR_MMA) ||
+                !mbar_wait(&v_full[s], u & 1, p.error, ERR_MMA)) { ok = false; break; }
+            tc_fence_after();
+            const unsigned p_addr = smem_u32(sm + OFF_P);
+            const unsigned v_addr = smem_u32(sm + OFF_V + s * KV_STAGE);
+#pragma unroll
+            for (int k = 0; k < BN / 16; ++k)                  // 16 keys per MMA: two 8-key groups of V
+                mma_ss(tmem_base + COL_O, desc_kmajor(p_addr + k * 32), desc_mnmajor(v_addr + k * 2048),
+                       idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+            tc_commit(&v_empty[s]);
+            tc_commit(p_empty);
+            tc_commit(o_done);
+        }
+    } else if (warp >= 2) {
+        // ----------------------------------------------------------------------- softmax
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                     // this thread's row = its TMEM lane
+        const int jj = r / p.G, hh = r - jj * p.G;
+        const bool row_ok = n_tiles > 0 && jj < ntok;
+        const int p_row = p_first + jj;
+        const int lo_row = p.window > 0 ? max(0, p_row - p.window + 1) : 0;
+        const unsigned lane_addr = tmem_base + ((unsigned)(quarter * 32) << 16);
+        pdl_wait();
+        // Q row into swizzled shared memory (chunk c of row r sits at chunk c ^ (r & 7))
+        {
+            const bf16* src = p.q + (size_t)(q_begin + tok0 + jj) * p.q_stride + (size_t)(g * p.G + hh) * HD;
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb)
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (row_ok) v = *reinterpret_cast<const uint4*>(src + kb * 64 + c * 8);
+                    *reinterpret_cast<uint4*>(sm + OFF_Q + kb * (BM * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+                }
+            proxy_fence();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(q_ready);
+        }
+        float m = -INFINITY, l = 0.f;                          // m: the maximum the output is scaled to
+        bool ok = true;
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            const int t = t_begin + j;
+            if (!mbar_wait(s_full, j & 1, p.error, ERR_SOFTMAX)) { ok = false; break; }
+            tc_fence_after();
+            float s[BN];
+            tmem_ld64_issue(lane_addr + COL_S, s);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty);                // the tensor core may write the next tile's scores
+            if (p.window > 0 || t * BN + BN - 1 > p_row || !row_ok) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const int key = t * BN + i;
+                    s[i] = (row_ok && key <= p_row && key >= lo_row) ? s[i] : -INFINITY;
+                }
+            }
+            // four independent chains each for the maximum and the sum: one thread owns the whole
+            // row, and a single chain of 64 dependent operations would leave the scheduler idle
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < BN; i += 4) {
+                mx4[0] = fmaxf(mx4[0], s[i]); mx4[1] = fmaxf(mx4[1], s[i + 1]);
+                mx4[2] = fmaxf(mx4[2], s[i + 2]); mx4[3] = fmaxf(mx4[3], s[i + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
+            // The reference maximum moves only when the row's maximum has outgrown it by 2^8
+            // (probabilities up to 256 are exact enough in bf16 and harmless in fp32 sums);
+            // then the output in tensor memory and the sum are brought to the new reference.
+            float factor = 1.f;
+            if (mx > m + RESCALE_STEP || (m == -INFINITY && mx != -INFINITY)) {
+                factor = m == -INFINITY ? 0.f : ex2(m - mx);
+                m = mx;
+            }
+            const bool rescale = factor != 1.f && j > 0;
+            if (__any_sync(0xffffffffu, rescale)) {
+                if (!mbar_wait(o_done, (j - 1) & 1, p.error, ERR_SOFTMAX)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 16) {
+                    float v[16];
+                    tmem_ld16_issue(lane_addr + COL_O + c0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] *= factor;
+                    tmem_st16(lane_addr + COL_O + c0, v);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+            }
+            l *= factor;
+            const float m_use = m == -INFINITY ? 0.f : m;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < BN; i += 4) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    s[i + k] = ex2(fmaf(s[i + k], p.scale_log2, -m_use));
+                    sum4[k] += s[i + k];
+                }
+            }
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            // P row (bf16) into the A operand of P V
+            if (!mbar_wait(p_empty, (j & 1) ^ 1, p.error, ERR_SOFTMAX)) { ok = false; break; }
+            {
+                unsigned char* prow = sm + OFF_P + r * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    uint4 w;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(s[c * 8 + 2 * i], s[c * 8 + 2 * i + 1]);
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) << 4)) = w;
+                }
+            }
+            // keys no row of the tile sees (past the last position, or before the window): whatever
+            // the cache holds there must not reach P V, not even times zero; their V rows are
+            // cleared (threads r < 64 each take one key row of the tile)
+            if (t * BN + BN - 1 > p_last || t * BN < lo_tile) {
+                const int st = j % NS, u = j / NS;
+                if (!mbar_wait(&v_full[st], u & 1, p.error, ERR_SOFTMAX)) { ok = false; break; }
+                if (r < BN && (t * BN + r > p_last || t * BN + r < lo_tile)) {
+#pragma unroll
+                    for (int kb = 0; kb < KB; ++kb) {
+                        uint4* vrow = reinterpret_cast<uint4*>(sm + OFF_V + st * KV_STAGE + kb * (BN * 128) + r * 128);
+#pragma unroll
+                        for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
+            proxy_fence();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        // the output of the last tile's P V, scaled by 1 / sum
+        if (ok && n_tiles > 0) ok = mbar_wait(o_done, (n_tiles - 1) & 1, p.error, ERR_SOFTMAX);
+        if (ok && n_tiles > 0) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = p.out + (size_t)(q_begin + tok0 + jj) * p.out_stride + (size_t)(g * p.G + hh) * HD;
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 16) {
+                float v[16];
+                tmem_ld16_issue(lane_addr + COL_O + c0, v);       // every lane of the warp takes part
+                tmem_ld_wait();
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint4 w;
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            h[i] = __floats2bfloat162_rn(v[c * 8 + 2 * i] * inv, v[c * 8 + 2 * i + 1] * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c * 8) = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host: tensor map
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(sym);
+    }
+    return fn;
+}
+struct MapKey {
+    const void* ptr; long long rows; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && box_rows == o.box_rows; }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        return reinterpret_cast<size_t>(k.ptr) ^ ((size_t)k.rows * 0x9E3779B97F4A7C15ull) ^ ((size_t)k.box_rows << 50);
+    }
+};
+// One layer of the cache, [page][K|V][kv head][slot][HD], seen as a matrix of HD-wide rows.
+int cache_map(const void* ptr, long long rows, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    std::lock_guard<std::mutex> lock(mu);
+    const MapKey key{ptr, rows, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiled fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    if (cache.size() > 1024) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+}  // namespace
+
+RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }
+RI_API int ri_attention_tc_head_dim() { return HD; }
+
+// 1 if this kernel takes the grouping and page size, else 0 (the caller then uses the
+// mma.sync kernel): the group must divide 128 rows, pages must be 8, 16, 32 or a multiple of 64 keys.
+RI_API int ri_attention_tc_supports(int Hq, int Hkv, int page_size) {
+    if (Hkv <= 0 || Hq % Hkv != 0) return 0;
+    const int G = Hq / Hkv;
+    if (G > BM || BM % G != 0) return 0;
+    return (page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0)) ? 1 : 0;
+}
+RI_API int ri_attention_tc_tokens_per_tile(int Hq, int Hkv) { return BM / (Hq / Hkv); }
+
+// Tiles are (entry, first token) pairs of 128 / (Hq/Hkv) tokens.  error: one int that a
+// timed-out wait sets (zero it before use).
+RI_API int ri_attention_prefill_tc(const void* q, int q_stride, void* out, int out_stride, const void* cache,
+                                   long long n_pages, const int* block_table, int table_stride, const int* cu_q,
+                                   const int* kv_len, const int* tile_entry, const int* tile_tok0, int n_tiles,
+                                   int Hq, int Hkv, int page_size, float scale, int window, int* error,
+                                   void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (!ri_attention_tc_supports(Hq, Hkv, page_size) || !error) return (int)cudaErrorInvalidValue;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    Params p;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.out_stride = out_stride;
+    p.block_table = block_table; p.table_stride = table_stride; p.cu_q = cu_q; p.kv_len = kv_len;
+    p.tile_entry = tile_entry; p.tile_tok0 = tile_tok0;
+    p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.tpt = BM / p.G; p.page_size = page_size;
+    p.box_rows = page_size < BN ? page_size : BN;
+    p.scale_log2 = scale * 1.4426950408889634f; p.window = window; p.error = error;
+    CUtensorMap map;
+    int st = cache_map(cache, n_pages * 2 * Hkv * page_size, p.box_rows, &map);
+    if (st != 0) return st;
+    RI_CHECKED(ri_launch(attention_tc_kernel, dim3(Hkv, n_tiles), dim3(THREADS), SMEM, (cudaStream_t)stream, map, p));
+    return ri_launch_status();
+}

@@ -266,6 +266,36 @@ def attention_prefill_bf16(q, out, cache, block_table, cu_q, kv_len, tile_entry,
                                         stream_ptr()), "attention_prefill_bf16")
 
 
+def tc_attention_supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prompt-attention kernel takes this geometry."""
+    if head_dim not in (64, 128):
+        return False
+    return bool(L.attention_tc(head_dim).ri_attention_tc_supports(num_heads, num_kv_heads, page_size))
+
+
+def tc_tokens_per_tile(num_heads: int, num_kv_heads: int) -> int:
+    return 128 // (num_heads // num_kv_heads)
+
+
+def attention_prefill_tc(q, out, cache, block_table, cu_q, kv_len, tile_entry, tile_tok0,
+                         num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                         window: Optional[int]) -> None:
+    """Prompt attention on tcgen05 tensor cores with TMA page fetches.  Tiles are (entry,
+    first token) pairs of `tc_tokens_per_tile` tokens each."""
+    _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim)
+    require_cuda(tile_entry, tile_tok0)
+    _i32(tile_entry, "tile_entry"); _i32(tile_tok0, "tile_tok0")
+    if out.stride(0) % 8 or out.data_ptr() % 16 or cache.data_ptr() % 16:
+        raise KernelError("attention_prefill_tc: out rows and the cache must be 16-byte aligned")
+    _ws, _counters, err = gemm_tc_state(q.device)
+    lib = L.attention_tc(head_dim)
+    check(lib.ri_attention_prefill_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), cache.shape[0],
+                                      _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_len),
+                                      _p(tile_entry), _p(tile_tok0), tile_entry.numel(), num_heads,
+                                      num_kv_heads, cache.shape[3], float(scale), int(window) if window else 0,
+                                      _p(err), stream_ptr()), "attention_prefill_tc")
+
+
 def decode_scratch_floats(entries: int, num_heads: int, head_dim: int, splits: int):
     return entries * num_heads * splits * head_dim, entries * num_heads * splits
 

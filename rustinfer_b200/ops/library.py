@@ -31,6 +31,8 @@ _SIGNATURES = {
     "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
     "ri_attention_mma_tokens_per_tile": [_I],
+    "ri_attention_prefill_tc": [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
+    "ri_attention_tc_supports": [_I, _I, _I],
     "ri_gemm_tc": [_P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
 }
@@ -119,6 +121,13 @@ def attention_mma(head_dim: int) -> ctypes.CDLL:
     return lib
 
 
+def attention_tc(head_dim: int) -> ctypes.CDLL:
+    """The tcgen05 attention kernel for prompt portions (head sizes 64 and 128)."""
+    if head_dim not in (64, 128):
+        raise KernelError(f"the tcgen05 attention kernel takes head sizes 64 and 128, got {head_dim}")
+    return _load(f"ri_attention_tc_hd{head_dim}", ["attention_tc.cu"], [f"RI_HEAD_DIM={head_dim}"])
+
+
 def build_all(head_dims) -> None:
     """Compile every library for the given head sizes (the ahead-of-time build check)."""
     core()
@@ -127,6 +136,8 @@ def build_all(head_dims) -> None:
         attention_plain(hd)
         if hd <= MMA_MAX_HEAD_DIM:
             attention_mma(hd)
+        if hd in (64, 128):
+            attention_tc(hd)
 
 
 launch_count = 0        # kernels of this package launched (or captured into a graph) so far

@@ -6,6 +6,7 @@ before it belong to the block, not to this part.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
@@ -63,8 +64,12 @@ class GQAAttention(Mixer):
         # bf16 runs on the tensor-core kernels (head sizes up to 256); fp32, and larger heads,
         # on the plain fp32-arithmetic kernel
         self.use_mma = ctx.dtype == torch.bfloat16 and self.hd <= L.MMA_MAX_HEAD_DIM
+        # prompt portions: the tcgen05 kernel where it takes the geometry, else the mma.sync one
+        self.use_tc = (self.use_mma and os.environ.get("RUSTINFER_B200_PREFILL_ATTENTION", "tc") != "mma"
+                       and K.tc_attention_supports(self.Hq, self.Hkv, self.hd, ctx.page_size))
         if self.use_mma:
-            self.tokens_per_tile = K.mma_tokens_per_tile(self.Hq, self.Hkv)
+            self.tokens_per_tile = (K.tc_tokens_per_tile(self.Hq, self.Hkv) if self.use_tc
+                                    else K.mma_tokens_per_tile(self.Hq, self.Hkv))
             self.attention_tile_rows = ()
             self.prefill_tile_rows = (self.tokens_per_tile,)
             key = ("decode_scratch", self.Hq, self.hd)
@@ -131,8 +136,9 @@ class GQAAttention(Mixer):
                                     self.scale, self.window, splits, self.part_o, self.part_lse)
         tile_entry, tile_tok0 = step.prefill_tiles[self.tokens_per_tile]
         if tile_entry.numel():
-            K.attention_prefill_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry,
-                                     tile_tok0, self.Hq, self.Hkv, self.hd, self.scale, self.window)
+            prefill = K.attention_prefill_tc if self.use_tc else K.attention_prefill_bf16
+            prefill(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
+                    self.Hq, self.Hkv, self.hd, self.scale, self.window)
         return self._project_out(out, residual)
 
     def _splits(self, n_decode: int, max_kv_len: int) -> int:

@@ -27,6 +27,17 @@ def tol(dtype):
     return 2e-6 if dtype == torch.float32 else 2 ** -8
 
 
+def close_attention(got, case, ref):
+    """bf16 attention: the output is rounded once (half an ulp of its size, 2^-9 relative) and
+    the probabilities were rounded to bf16 before they met the values (2^-9 relative each,
+    so at most 2^-9 of the largest |v| in the weighted mean): |err| <= 2^-9 (max|out| + max|v|)."""
+    ref = ref.double().cpu()
+    vmax = max(float(v.double().abs().max()) for v in case.v)
+    bound = 2 ** -9 * (float(ref.abs().max()) + vmax)
+    err = float((got.double().cpu() - ref).abs().max())
+    assert err <= bound, f"max err {err:.3e} vs bound {bound:.3e}"
+
+
 def close(got, ref, dtype, scale=None):
     ref = ref.double().cpu()
     scale = float(ref.abs().max()) if scale is None else scale
@@ -432,6 +443,60 @@ def test_attention_mma_finds_one_far_key(kernel):
             te, tq = _mma_tiles(case, k.mma_tokens_per_tile(Hq, Hkv), skip_decode=False)
             k.attention_prefill_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
                                      Hq, Hkv, hd, 1.0, None)
+        want = torch.cat([case.v[0][far, h // (Hq // Hkv)].double() for h in range(Hq)])
+        assert float((out.double().cpu()[0] - want).abs().max()) < 0.05, far
+
+
+# ------------------------------------------------ tcgen05 prompt attention (bf16, hd 64/128)
+TC_ATT_SHAPES = [(8, 2, 64, 16), (32, 8, 64, 16), (4, 4, 64, 8), (16, 1, 64, 32), (8, 2, 128, 16), (24, 3, 128, 64),
+                 (2, 2, 128, 8)]
+
+
+@pytest.mark.parametrize("Hq,Hkv,hd,page", TC_ATT_SHAPES)
+def test_attention_tc_prefill_ragged(Hq, Hkv, hd, page):
+    """Whole prompts, portions that start mid-page and mid-tile, one-token entries; unused
+    slots of the pages hold NaN, which must not leak through P V."""
+    k = K()
+    assert k.tc_attention_supports(Hq, Hkv, hd, page)
+    kv_lens = [1, 17, 64, 65, 130, 33, 16, 300, 515]
+    q_lens = [1, 17, 1, 2, 41, 33, 1, 129, 300]
+    case = PagedCase(BF, Hq, Hkv, hd, page, kv_lens, q_lens, seed=hd + Hq, poison=True)
+    out = torch.full_like(case.q_all, float("nan"))
+    te, tq = _mma_tiles(case, k.tc_tokens_per_tile(Hq, Hkv), skip_decode=False)
+    scale = 1 / math.sqrt(hd)
+    k.attention_prefill_tc(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                           Hq, Hkv, hd, scale, None)
+    close_attention(out, case, case.reference(scale))
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+
+
+@pytest.mark.parametrize("window", [1, 5, 16, 40, 100])
+def test_attention_tc_window(window):
+    Hq, Hkv, hd = 8, 2, 64
+    k = K()
+    case = PagedCase(BF, Hq, Hkv, hd, 8, [70, 9, 40, 200, 300], [30, 9, 1, 1, 150], seed=window)
+    out = torch.full_like(case.q_all, float("nan"))
+    te, tq = _mma_tiles(case, k.tc_tokens_per_tile(Hq, Hkv), skip_decode=False)
+    k.attention_prefill_tc(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                           Hq, Hkv, hd, 0.2, window)
+    close_attention(out, case, case.reference(0.2, window))
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+
+
+def test_attention_tc_finds_one_far_key():
+    Hq, Hkv, hd, page = 8, 2, 64, 16
+    k = K()
+    for far in (0, 15, 16, 63, 64, 255, 300, 310):
+        case = PagedCase(BF, Hq, Hkv, hd, page, [311], [1], seed=far, poison=True)
+        kk = case.k[0].double()
+        rows = [kk[far, h // (Hq // Hkv)] / kk[far, h // (Hq // Hkv)].norm() * 60.0 for h in range(Hq)]
+        case.q_all = torch.cat(rows).to(BF).reshape(1, Hq * hd).to(dev())
+        out = torch.full_like(case.q_all, float("nan"))
+        te, tq = _mma_tiles(case, k.tc_tokens_per_tile(Hq, Hkv), skip_decode=False)
+        k.attention_prefill_tc(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                               Hq, Hkv, hd, 1.0, None)
         want = torch.cat([case.v[0][far, h // (Hq // Hkv)].double() for h in range(Hq)])
         assert float((out.double().cpu()[0] - want).abs().max()) < 0.05, far
 
