@@ -26,6 +26,7 @@ class Decoder:
         self.embed_table: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self.head_is_tied = False
+        self.chained = None
         for i, e in enumerate(spec.run_order):
             mixer = self.blocks[e.layer].mixer
             if e.cache_of is not None:
@@ -90,12 +91,17 @@ class Decoder:
             for role, part in block.roles().items():
                 part.load({n: tensors[ls.names[role] + n] for n in part.param_decls()
                            if ls.names[role] + n in tensors})
+        # few-token steps of a decoder of the usual shape run their products chained
+        from .chained_decoder import ChainedDecoder
+        self.chained = ChainedDecoder.build(self)
 
     # --------------------------------------------------------------------------- run
     def forward(self, step: StepContext, caches: List, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the tokens of `step`; returns fp32 logits [rows, vocab] at `logit_rows`
         (token indices, int32, device), or None when no logits are wanted."""
         s = self.spec
+        if self.chained is not None and self.chained.takes(step):
+            return self.chained.forward(step, caches, logit_rows)
         h = torch.empty((step.num_tokens, s.hidden_size), dtype=torch.float32, device=self.ctx.device)
         K.embed_gather(step.token_ids[: step.num_tokens], self.embed_table, h)
         hidden = Hidden(h, None)

@@ -2,7 +2,8 @@
 (device, dtype, layout, sizes) and raises instead of computing something wrong."""
 from __future__ import annotations
 
-from typing import Optional
+import ctypes
+from typing import Dict, Optional, Sequence
 
 import torch
 
@@ -205,6 +206,119 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
         raise KernelError("gemm_tc: the split-K workspace is too small for this plan")
     check(L.gemm_tc().ri_gemm_tc(_p(x), _p(w), M, N, Kd, _p(out), out.stride(0), epilogue, swap, bn, splits,
                                  a_box, _p(ws), _p(counters), _p(err), stream_ptr()), "gemm_tc")
+
+
+class _ChainPhase(ctypes.Structure):
+    _fields_ = [("w", ctypes.c_void_p), ("N", ctypes.c_int), ("K", ctypes.c_int), ("x_kind", ctypes.c_int),
+                ("ld_x", ctypes.c_int), ("x", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
+                ("norm_w_dtype", ctypes.c_int), ("eps", ctypes.c_float), ("out_kind", ctypes.c_int),
+                ("ld_out", ctypes.c_int), ("out", ctypes.c_void_p)]
+
+
+class _ChainRope(ctypes.Structure):
+    _fields_ = [("qkv", ctypes.c_void_p), ("ld", ctypes.c_int), ("positions", ctypes.c_void_p),
+                ("cos_t", ctypes.c_void_p), ("sin_t", ctypes.c_void_p), ("slot_of_token", ctypes.c_void_p),
+                ("q_out", ctypes.c_void_p), ("ld_q", ctypes.c_int), ("cache", ctypes.c_void_p),
+                ("Hq", ctypes.c_int), ("Hkv", ctypes.c_int), ("hd", ctypes.c_int), ("rot", ctypes.c_int),
+                ("page_size", ctypes.c_int)]
+
+
+CHAIN_ADD_F32, CHAIN_SILU_BF16, CHAIN_BF16 = 0, 1, 2
+CHAIN_MAX_TOKENS, CHAIN_MAX_PRODUCTS = 32, 6
+
+
+class ChainProduct:
+    """One product of a `decode_chain`: out (+)= f(x) w^T.  `x` is a bf16 matrix [M, K], or,
+    with `norm=(weight, eps)`, the fp32 stream [M, K] whose RMS norm times `weight` is the
+    operand.  `out_kind`: CHAIN_ADD_F32 adds into an fp32 matrix; CHAIN_SILU_BF16 stores
+    silu(gate) * up of a weight whose rows alternate gate_j, up_j into bf16 [M, N/2];
+    CHAIN_BF16 stores bf16 [M, N]."""
+
+    def __init__(self, w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, out_kind: int, norm=None):
+        self.w, self.x, self.out, self.out_kind, self.norm = w, x, out, out_kind, norm
+        N, Kd = w.shape
+        want_x = torch.float32 if norm is not None else torch.bfloat16
+        cols = N // 2 if out_kind == CHAIN_SILU_BF16 else N
+        want_o = torch.float32 if out_kind == CHAIN_ADD_F32 else torch.bfloat16
+        if (w.dtype != torch.bfloat16 or not w.is_contiguous() or x.dtype != want_x or x.shape[1] != Kd
+                or x.stride(1) != 1 or out.dtype != want_o or out.shape[1] != cols or out.stride(1) != 1
+                or x.shape[0] != out.shape[0] or (norm is not None and norm[0].numel() != Kd)):
+            raise KernelError(f"decode_chain: product w{tuple(w.shape)} x{tuple(x.shape)} {x.dtype} "
+                              f"out{tuple(out.shape)} {out.dtype} does not fit together")
+
+    def fill(self, c: "_ChainPhase") -> None:
+        c.w, c.N, c.K = self.w.data_ptr(), self.w.shape[0], self.w.shape[1]
+        c.x, c.ld_x, c.x_kind = self.x.data_ptr(), self.x.stride(0), 1 if self.norm is not None else 0
+        if self.norm is not None:
+            c.norm_w, c.norm_w_dtype, c.eps = self.norm[0].data_ptr(), dtype_code(self.norm[0].dtype), float(self.norm[1])
+        else:
+            c.norm_w, c.norm_w_dtype, c.eps = None, 0, 0.0
+        c.out, c.ld_out, c.out_kind = self.out.data_ptr(), self.out.stride(0), self.out_kind
+
+
+class ChainRope:
+    """The tail of a chain whose last product added q, k, v rows into the fp32 matrix `qkv`
+    [M, (Hq + 2 Hkv) * hd]: rotate q and k, write q (bf16) into `q_out`, k and v into the pages
+    of `cache` at `slot_of_token` (-1: not written), and put `qkv` back to zero."""
+
+    def __init__(self, qkv, positions, cos_t, sin_t, slot_of_token, q_out, cache, Hq, Hkv, hd, rot):
+        self.__dict__.update(locals())
+        if qkv.dtype != torch.float32 or q_out.dtype != torch.bfloat16 or qkv.shape[1] != (Hq + 2 * Hkv) * hd \
+                or q_out.shape[1] != Hq * hd or (cache is not None and (cache.dtype != torch.bfloat16 or cache.dim() != 5
+                                                                      or cache.shape[2] != Hkv or cache.shape[4] != hd)):
+            raise KernelError("decode_chain: the rotary tail's buffers do not fit together")
+
+    def fill(self, c: "_ChainRope") -> None:
+        c.qkv, c.ld = self.qkv.data_ptr(), self.qkv.stride(0)
+        c.positions, c.cos_t, c.sin_t = self.positions.data_ptr(), self.cos_t.data_ptr(), self.sin_t.data_ptr()
+        c.slot_of_token = self.slot_of_token.data_ptr() if self.slot_of_token is not None else None
+        c.q_out, c.ld_q = self.q_out.data_ptr(), self.q_out.stride(0)
+        c.cache = self.cache.data_ptr() if self.cache is not None else None
+        c.Hq, c.Hkv, c.hd, c.rot = self.Hq, self.Hkv, self.hd, self.rot
+        c.page_size = self.cache.shape[3] if self.cache is not None else 1
+
+
+_chain_state: Dict[torch.device, torch.Tensor] = {}
+
+
+def _chain_barrier(device: torch.device) -> torch.Tensor:
+    bar = _chain_state.get(device)
+    if bar is None:
+        bar = torch.zeros(2, dtype=torch.int32, device=device)
+        _chain_state[device] = bar
+    return bar
+
+
+def _chain_array(products: Sequence[ChainProduct]):
+    arr = (_ChainPhase * len(products))()
+    for c, pr in zip(arr, products):
+        pr.fill(c)
+    return arr
+
+
+def decode_chain_fits(products: Sequence[ChainProduct], tokens: int, num_sms: int) -> bool:
+    """Whether `decode_chain` can run these products for this many tokens."""
+    if not 1 <= len(products) <= CHAIN_MAX_PRODUCTS or not 1 <= tokens <= CHAIN_MAX_TOKENS:
+        return False
+    lib = L.gemm_tc()
+    lib.ri_decode_chain_fits.restype = ctypes.c_int
+    return lib.ri_decode_chain_fits(ctypes.cast(_chain_array(products), ctypes.c_void_p), len(products),
+                                    tokens, num_sms) > 0
+
+
+def decode_chain(products: Sequence[ChainProduct], rope: Optional[ChainRope], tokens: int, num_sms: int) -> None:
+    """Run the products one after the other for the first `tokens` rows of their matrices in
+    one cooperative kernel (see csrc/decode_chain.cu), then the rotary tail if given."""
+    dev = products[0].w.device
+    arr = _chain_array(products)
+    rp = None
+    if rope is not None:
+        rs = _ChainRope()
+        rope.fill(rs)
+        rp = ctypes.cast(ctypes.pointer(rs), ctypes.c_void_p)
+    _, _, err = gemm_tc_state(dev)
+    check(L.gemm_tc().ri_decode_chain(ctypes.cast(arr, ctypes.c_void_p), len(products), rp, tokens,
+                                      _p(_chain_barrier(dev)), _p(err), num_sms, stream_ptr()), "decode_chain")
 
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "ri_attention_prefill_tc": [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "ri_attention_tc_supports": [_I, _I, _I],
     "ri_gemm_tc": [_P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P],
+    "ri_decode_chain": [_P, _I, _P, _I, _P, _P, _I, _P],
+    "ri_decode_chain_fits": [_P, _I, _I, _I],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
 }
 
@@ -93,7 +95,7 @@ def attention_plain(head_dim: int) -> ctypes.CDLL:
 
 
 def gemm_tc() -> ctypes.CDLL:
-    lib = _load("ri_gemm_tc", ["gemm_tc.cu"])
+    lib = _load("ri_gemm_tc", ["gemm_tc.cu", "decode_chain.cu"])
     kb = os.environ.get("RUSTINFER_B200_STREAM_KB")
     if kb and not getattr(lib, "_budget_set", False):
         lib.ri_gemm_tc_set_stream_budget.argtypes = [_I]

@@ -110,7 +110,6 @@ class GQAAttention(Mixer):
     def forward(self, x: torch.Tensor, step: StepContext, cache: PagedLayerCache,
                 residual: Optional[torch.Tensor] = None):
         """Returns the sublayer's output, or None when it was added into `residual`."""
-        T = x.shape[0]
         g = step.groups[cache.group]
         qkv = self.qkv(x, out_dtype=self.ctx.dtype)
         writes = self.own_kv and cache.writes
@@ -122,13 +121,21 @@ class GQAAttention(Mixer):
                            self.position.rotary_dim)
         else:
             raise NotImplementedError("attention without a rotary encoding has no cache-write kernel yet")
-        q = qkv[:, : self.Hq * self.hd]
-        out = torch.empty((T, self.Hq * self.hd), dtype=self.ctx.dtype, device=x.device)
+        return self._project_out(self.attend(qkv[:, : self.Hq * self.hd], step, cache), residual)
+
+    def attend(self, q: torch.Tensor, step: StepContext, cache: PagedLayerCache,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Attention of the rotated queries q [T, Hq*hd] (unit column stride) over the cache, whose
+        pages already hold this step's keys and values: [T, Hq*hd] (into `out` if given)."""
+        T = step.num_tokens
+        g = step.groups[cache.group]
+        if out is None:
+            out = torch.empty((T, self.Hq * self.hd), dtype=self.ctx.dtype, device=q.device)
         if not self.use_mma:
             tile_entry, tile_q0 = step.tiles[16]
             K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
                               self.Hq, self.Hkv, self.hd, self.scale, self.window)
-            return self._project_out(out, residual)
+            return out
         if step.num_decode:
             splits = self._splits(step.num_decode, step.max_kv_len)
             K.attention_decode_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len,
@@ -139,7 +146,7 @@ class GQAAttention(Mixer):
             prefill = K.attention_prefill_tc if self.use_tc else K.attention_prefill_bf16
             prefill(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,
                     self.Hq, self.Hkv, self.hd, self.scale, self.window)
-        return self._project_out(out, residual)
+        return out
 
     def _splits(self, n_decode: int, max_kv_len: int) -> int:
         """Ranges each decoding request's keys are cut into.  A few CTAs sit on an SM (the

@@ -231,6 +231,82 @@ def test_rope_scatter(dt, Hq, Hkv, hd, rot, page):
     assert torch.equal(cache.double().cpu()[untouched], want[untouched])
 
 
+@pytest.mark.parametrize("M,hidden,inter,Hq,Hkv,hd,rot,page", [
+    (8, 2048, 8192, 32, 8, 64, 64, 16),          # the shapes of a 1B decoder
+    (5, 272, 552, 6, 2, 48, 32, 8),               # nothing a power of two, part of each head rotates
+    (19, 520, 1040, 5, 5, 32, 32, 4),             # more than 16 tokens: the wider tile
+    (1, 136, 96, 3, 1, 16, 16, 16),
+])
+def test_decode_chain(M, hidden, inter, Hq, Hkv, hd, rot, page):
+    """Five steps of a decoder layer's seam in one kernel: attention output times Wo into the
+    stream, norm + gate/up + SiLU, down into the stream, norm + q,k,v, rotary + cache write;
+    against the plain formulas in float64 from the same bf16 weights."""
+    torch.manual_seed(M + hidden)
+    k = K()
+    d = dev()
+    qdim, width = Hq * hd, (Hq + 2 * Hkv) * hd
+    bf = lambda t: t.bfloat16().to(d)
+    wo, wg, wu = torch.randn(hidden, qdim) / qdim ** 0.5, torch.randn(inter, hidden) / hidden ** 0.5, torch.randn(inter, hidden) / hidden ** 0.5
+    wd, wqkv = torch.randn(hidden, inter) / inter ** 0.5, torch.randn(width, hidden) / hidden ** 0.5
+    n1, n2 = 1 + 0.2 * torch.randn(hidden), 1 + 0.2 * torch.randn(hidden)
+    wo_d, wd_d, wqkv_d = bf(wo), bf(wd), bf(wqkv)
+    wgu_d = torch.stack([wg, wu], dim=1).reshape(2 * inter, hidden).bfloat16().to(d)     # rows alternate gate, up
+    n1_d, n2_d = bf(n1), n2.to(d)                                                        # one norm weight in each dtype
+    attn = torch.randn(M, qdim)
+    h0 = torch.randn(M, hidden) * 2
+    rows = 32                                                                            # buffers hold more rows than are used
+    attn_d = torch.zeros(rows, qdim, dtype=torch.bfloat16, device=d); attn_d[:M] = bf(attn)
+    h_d = torch.zeros(rows, hidden, dtype=torch.float32, device=d); h_d[:M] = h0.to(d)
+    m_d = torch.full((rows, inter), 9.0, dtype=torch.bfloat16, device=d)
+    qkv_d = torch.zeros(rows, width, dtype=torch.float32, device=d)
+    q_d = torch.full((rows, qdim), 9.0, dtype=torch.bfloat16, device=d)
+    pages, maxpos = 12, 300
+    pos = torch.randint(0, maxpos, (rows,), dtype=torch.int32)
+    c, s_ = _rope_tables(maxpos, rot)
+    slots = torch.randperm(pages * page)[:rows].to(torch.int32)
+    if M > 2:
+        slots[2] = -1                                                                    # a token that is not stored
+    cache = torch.full((pages, 2, Hkv, page, hd), 7.0, dtype=torch.bfloat16, device=d)
+    products = [k.ChainProduct(wo_d, attn_d, h_d, k.CHAIN_ADD_F32),
+                k.ChainProduct(wgu_d, h_d, m_d, k.CHAIN_SILU_BF16, norm=(n1_d, 1e-5)),
+                k.ChainProduct(wd_d, m_d, h_d, k.CHAIN_ADD_F32),
+                k.ChainProduct(wqkv_d, h_d, qkv_d, k.CHAIN_ADD_F32, norm=(n2_d, 3e-6))]
+    rope = k.ChainRope(qkv_d, pos.to(d), c.float().to(d), s_.float().to(d), slots.to(d), q_d, cache, Hq, Hkv, hd, rot)
+    assert k.decode_chain_fits(products, M, 148)
+    for _ in range(2):                                       # twice: the barrier and the q,k,v buffer reset themselves
+        h_d[:M] = h0.to(d)
+        k.decode_chain(products, rope, M, 148)
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(d) == 0
+    # ---- the same in float64 from the rounded weights
+    D = lambda t: t.double().cpu()
+    h1 = h0.double() + D(bf(attn)) @ D(wo_d).T
+    x1 = P.rmsnorm(h1, D(n1_d), 1e-5)
+    mid = P.swiglu(x1 @ D(bf(wg)).T, x1 @ D(bf(wu)).T)
+    close(m_d[:M], mid, torch.bfloat16)
+    assert torch.all(m_d[M:] == 9.0)
+    h2 = h1 + D(m_d[:M]) @ D(wd_d).T                        # from the kernel's own rounded intermediate
+    close(h_d[:M], h2, torch.bfloat16)
+    x2 = P.rmsnorm(D(h_d[:M]), D(n2_d), 3e-6)
+    qkv = (x2 @ D(wqkv_d).T).view(M, Hq + 2 * Hkv, hd)
+    f = P.rope_inv_freq(rot, 10000.0, None)
+    rotated = torch.cat([P.rope_rotate(qkv[..., :rot], pos[:M], f), qkv[..., rot:]], dim=-1)
+    scale = float(qkv.abs().max())
+    close(q_d[:M].view(M, Hq, hd), rotated[:, :Hq], torch.bfloat16, scale=scale)
+    assert torch.all(q_d[M:] == 9.0)
+    want = torch.full((pages, 2, Hkv, page, hd), 7.0, dtype=torch.float64)
+    for t in range(M):
+        if slots[t] < 0:
+            continue
+        pg, off = int(slots[t]) // page, int(slots[t]) % page
+        want[pg, 0, :, off] = rotated[t, Hq: Hq + Hkv]
+        want[pg, 1, :, off] = qkv[t, Hq + Hkv:]
+    close(cache, want, torch.bfloat16, scale=scale)
+    untouched = want == 7.0
+    assert torch.equal(cache.double().cpu()[untouched], want[untouched])
+    assert torch.count_nonzero(qkv_d) == 0                   # left at zero for the next chain
+
+
 class PagedCase:
     """A ragged batch laid out in a paged cache by hand, for the attention kernels."""
 

@@ -18,8 +18,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 # max |engine - plain| / max |plain| over the compared logits.  fp32: measured 0.6e-6 to
 # 2e-6 on these models (sums of a few hundred fp32 products against float64).  bf16: the
-# engine rounds activations to 8 bits of mantissa between ops, measured 0.3e-2 to 2e-2.
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# engine rounds activations, keys and values to 8 bits of mantissa, and these models are made
+# sharp (one score stands out by design), so a rounding of q or k moves a whole softmax row.
+# Measured over 24 sequences a model, cut into portions, with the products run one by one and
+# chained alike: A mean 1.0e-2, worst 2.1e-2; B mean 2.4e-2, 90th percentile 3.3e-2, worst
+# 4.3e-2; C mean 0.4e-2, worst 0.7e-2.  Which roundings meet at the sharp position differs from
+# cut to cut, so the bound sits above the worst realisation seen; the faults these tests are
+# made for (a wrong key, page or position at the sharp score) move the logits by tenths.
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
 # The same positions through a different cut of the work, engine against engine: fp32 is
 # bit-identical by construction of the kernels and asserted as such.  In bf16 a decoded
 # token and a prompt portion go through different kernels (split-KV decode, tiled prefill)
