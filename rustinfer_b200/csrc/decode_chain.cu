@@ -27,6 +27,30 @@
 #include "tc_primitives.cuh"
 #include <cuda.h>
 
+// One product of a chain, as the caller describes it.
+struct RiChainPhase {
+    const void* w;              // bf16 [N][K], K a multiple of 8, 16-byte aligned
+    int N, K;
+    int x_kind;                 // 0: x is bf16 [M][ld_x]; 1: x is the fp32 stream [M][ld_x] and the
+    int ld_x;                   //    operand is x * norm_w * rsqrt(mean(x^2) + eps)
+    int x_rows;                 // rows the matrix x really has (a TMA box reads 8, 16 or 32 of them)
+    const void* x;
+    const void* norm_w;
+    int norm_w_dtype;
+    float eps;
+    int out_kind;               // 0: fp32 out += product; 1: bf16 out[M][N/2] = silu(gate) * up over
+    int ld_out;                 //    alternating weight rows; 2: bf16 out = product
+    void* out;
+};
+
+struct RiChainRope {
+    float* qkv; int ld;
+    const int* positions; const float* cos_t; const float* sin_t; const int* slot_of_token;
+    void* q_out; int ld_q;
+    void* cache;
+    int Hq, Hkv, hd, rot, page_size;
+};
+
 namespace {
 using namespace ri_tc;
 constexpr int BM = 128, BK = 64, THREADS = 192;
@@ -36,6 +60,7 @@ constexpr int STAGE_BYTES = SUBS * SUB_BYTES;
 constexpr int KSTEP = SUBS * BK;               // K columns per stage
 constexpr int MAX_PHASES = 6, MAX_STAGES = 6;
 constexpr int HEAD_BYTES = 1024;               // barriers and row scales in front of the ring
+constexpr int ROW_STAGE_BYTES = 64 * 1024;     // most bytes of fp32 stream rows staged at a time
 constexpr int SMEM_LIMIT = 225 * 1024;
 
 enum XKind { X_BF16 = 0, X_NORM = 1 };
@@ -70,18 +95,34 @@ struct Rope {
 
 struct Params {
     int M, n_phases, stages, xs_off;
+    int x_kb_bytes;             // bytes of one 64-column block of the activation operand (1024 when rows 8..15 alias rows 0..7)
+    int stage_off, stage_rows;  // where rows of the fp32 stream are staged, and how many at a time
+    int nw_off;                 // where the norm weight is staged
     Phase ph[MAX_PHASES];
     Rope rope;
     unsigned* grid_bar;         // [0] arrivals, [1] exits; zero between launches
     int* error;
 };
 
-struct Maps { CUtensorMap m[MAX_PHASES]; };
+struct Maps { CUtensorMap m[MAX_PHASES]; CUtensorMap x[MAX_PHASES]; };   // weights; bf16 activation matrices
 
 __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+
+__device__ __forceinline__ void bulk_load(void* smem, const void* g, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem)), "l"(g), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(unsigned addr, float (&v)[4]) {
+    unsigned r[4];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // All CTAs have arrived `target` times in total.  One thread spins (bounded).
@@ -103,10 +144,10 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
     uint64_t* empty = full + MAX_STAGES;                         // [MAX_STAGES]
     uint64_t* x_ready = empty + MAX_STAGES;
     uint64_t* acc_full = x_ready + 1;
-    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_full + 1);
+    uint64_t* x_land = acc_full + 1;                              // TMA copies of activations have landed
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(x_land + 1);
     unsigned* go_slot = tmem_slot + 1;                            // 1 while the grid barriers hold
     float* row_scale = reinterpret_cast<float*>(base + 384);     // [BN]
-    float* row_part = row_scale + BN;                            // [4 warps][BN]
     unsigned char* ring = base + HEAD_BYTES;
     unsigned char* xs = base + p.xs_off;
     constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
@@ -118,6 +159,7 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(x_ready, 4);
         mbar_init(acc_full, 1);
+        mbar_init(x_land, 1);
         *go_slot = 1;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -161,7 +203,11 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
         // one scalar thread feeds the tensor core: descriptors are made once and stepped by adds,
         // the ring position is counted, not divided
-        const uint64_t desc_ring = smem_desc(smem_u32(ring)), desc_xs = smem_desc(smem_u32(xs));
+        // with at most 8 tokens the second group of 8 rows of the operand is the first one again
+        // (group stride 0), which halves the activation region
+        const uint64_t desc_ring = smem_desc(smem_u32(ring));
+        const uint64_t desc_xs = p.x_kb_bytes == 1024 ? (smem_desc(smem_u32(xs)) & ~(0x3fffull << 32)) : smem_desc(smem_u32(xs));
+        const unsigned x_step = (unsigned)p.x_kb_bytes >> 4;
         bool ok = true;
         int s = 0, n = 0;
         unsigned par = 0;
@@ -183,9 +229,9 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k)
                             mma_bf16_ss(tmem_base, da + (uint64_t)(h * (SUB_BYTES >> 4) + k * 2),
-                                        db + (uint64_t)(h * ((BN * BK * 2) >> 4) + k * 2), idesc, (i > 0 || h > 0 || k > 0) ? 1u : 0u);
+                                        db + (uint64_t)(h * x_step + k * 2), idesc, (i > 0 || h > 0 || k > 0) ? 1u : 0u);
                     tc_commit(&empty[s]);
-                    db += (uint64_t)(SUBS * ((BN * BK * 2) >> 4));
+                    db += (uint64_t)(SUBS * x_step);
                     if (++s == STAGES) { s = 0; par ^= 1u; }
                 }
                 if (ok) tc_commit(acc_full);
@@ -204,7 +250,7 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
         const int te = threadIdx.x - 64, M = p.M;
         const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16);
         bool ok = true;
-        int n = 0;
+        int n = 0, xl = 0;                                // items done; TMA batches of activations landed
         pdl_wait();                                       // everything but the weights belongs to earlier kernels till now
         for (int ph = 0; ph < p.n_phases; ++ph) {
             const Phase& P = p.ph[ph];
@@ -215,162 +261,112 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 ok = ok && *go_slot;
             }
-            bool scaled = false;
+            bool nw_here = false;                             // this product's norm weight is staged
             for (int item = blockIdx.x; item < P.tiles * P.splits; item += G, ++n) {
                 const int tile = item % P.tiles, st0 = (item / P.tiles) * P.per;
                 const int kb0 = st0 * SUBS, n_kb = min(P.per, kblocks - st0) * SUBS;   // in 64-column blocks
                 if (!ok) continue;
-                // ---- the activation operand of this K slice: the 16-byte chunk c of token r in
-                // k-block kbl sits at chunk c ^ (r & 7) of its 128-byte row (the swizzle the
-                // tensor core expects).  Every load of a batch is issued before the first use:
-                // under a full weight stream one trip to L2 takes well over a microsecond.
+                // ---- the activation operand of this K slice, in the layout the tensor core
+                // reads: 64-column blocks of 128-byte rows, 16-byte chunk c of row r at c ^ (r & 7).
+                // This code runs once per product and launch, from a cold instruction cache and
+                // against a full weight stream, where each trip to L2 takes well over a microsecond:
+                // the copies are TMA's (one thread issues them), the loops are short and rolled.
+                if (threadIdx.x == 64) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 if (P.x_kind == X_BF16) {
-                    const bf16* xb = reinterpret_cast<const bf16*>(P.x);
-                    const int total = M * n_kb * 8;
-                    for (int i0 = te; i0 < total; i0 += 128 * 8) {
-                        uint4 v[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int idx = i0 + 128 * i, rest = idx >> 3;
-                            const int kbl = rest % n_kb, r = rest / n_kb;
-                            const int k = (kb0 + kbl) * BK + (idx & 7) * 8;
-                            v[i] = make_uint4(0u, 0u, 0u, 0u);
-                            if (idx < total && k < P.K) v[i] = __ldcg(reinterpret_cast<const uint4*>(xb + (size_t)r * P.ld_x + k));
-                        }
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int idx = i0 + 128 * i, rest = idx >> 3, c = idx & 7;
-                            const int kbl = rest % n_kb, r = rest / n_kb;
-                            if (idx < total)
-                                *reinterpret_cast<uint4*>(xs + (size_t)kbl * (BN * BK * 2) + r * 128 + ((c ^ (r & 7)) << 4)) = v[i];
-                        }
+                    if (threadIdx.x == 64) {
+                        mbar_expect_tx(x_land, (unsigned)(n_kb * p.x_kb_bytes));
+                        for (int kbl = 0; kbl < n_kb; ++kbl)
+                            tma_load_2d(xs + (size_t)kbl * p.x_kb_bytes, &maps.x[ph], x_land, (kb0 + kbl) * BK, 0);
                     }
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(x_ready);
+                    ok = mbar_wait(x_land, xl & 1, p.error, ERR_CHAIN_EPILOGUE);
+                    ++xl;
                 } else {
-                    // the fp32 stream times the norm weight; the same pass over whole rows gives
-                    // the sum of squares (needed once per product), so nothing is read twice
+                    // rows of the fp32 stream are staged whole: the sum of squares needs all of a
+                    // row, the operand only this slice of it, times the norm weight (the RMS scale
+                    // is applied to the accumulator later).  A warp owns a row.
                     const float* hs = reinterpret_cast<const float*>(P.x);
+                    float* stg = reinterpret_cast<float*>(base + p.stage_off);
+                    unsigned char* nws = base + p.nw_off;
                     const int upr = P.K >> 3;                               // units of 8 floats in a row
                     const int k_lo = kb0 * BK, k_hi = (kb0 + n_kb) * BK;
-                    constexpr int RG = 8, UB = 2;                           // rows and units per batch
-                    for (int r0 = 0; r0 < M; r0 += RG) {
-                        float ss[RG];
-#pragma unroll
-                        for (int j = 0; j < RG; ++j) ss[j] = 0.f;
-                        const int u_end = scaled ? min(upr, k_hi >> 3) : upr;      // later items only need their slice
-                        for (int u0 = (scaled ? (k_lo >> 3) : 0) + te; u0 < u_end; u0 += 128 * UB) {
-                            float4 a[RG][UB], b[RG][UB];
-                            float w[UB][8];
-#pragma unroll
-                            for (int i = 0; i < UB; ++i) {
-                                const int u = u0 + 128 * i, k = u * 8;
-#pragma unroll
-                                for (int j = 0; j < RG; ++j) {
-                                    a[j][i] = make_float4(0.f, 0.f, 0.f, 0.f); b[j][i] = a[j][i];
-                                    if (u < u_end && r0 + j < M) {
-                                        const float* hr = hs + (size_t)(r0 + j) * P.ld_x + k;
-                                        a[j][i] = __ldcg(reinterpret_cast<const float4*>(hr));
-                                        b[j][i] = __ldcg(reinterpret_cast<const float4*>(hr + 4));
-                                    }
-                                }
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) w[i][e] = 0.f;
-                                if (u < u_end && k >= k_lo && k < k_hi) {
+                    const unsigned nw_bytes = (unsigned)P.K * (P.norm_w_bf16 ? 2u : 4u);
+                    for (int r0 = 0; r0 < M && ok; r0 += p.stage_rows) {
+                        const int rows = min(p.stage_rows, M - r0);
+                        if (threadIdx.x == 64) {
+                            mbar_expect_tx(x_land, (unsigned)rows * P.K * 4u + (nw_here ? 0u : nw_bytes));
+                            for (int r = 0; r < rows; ++r)
+                                bulk_load(stg + (size_t)r * P.K, hs + (size_t)(r0 + r) * P.ld_x, (unsigned)P.K * 4u, x_land);
+                            if (!nw_here) bulk_load(nws, P.norm_w, nw_bytes, x_land);
+                        }
+                        nw_here = true;
+                        ok = mbar_wait(x_land, xl & 1, p.error, ERR_CHAIN_EPILOGUE);
+                        ++xl;
+                        for (int r = quarter; r < rows && ok; r += 4) {
+                            const float* row = stg + (size_t)r * P.K;
+                            const int rr = r0 + r;
+                            float ss = 0.f;
+                            for (int u = lane; u < upr; u += 32) {
+                                const int k = u * 8;
+                                const float4 x0 = *reinterpret_cast<const float4*>(row + k);
+                                const float4 x1 = *reinterpret_cast<const float4*>(row + k + 4);
+                                ss += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w
+                                    + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
+                                if (k >= k_lo && k < k_hi) {
+                                    float w[8];
                                     if (P.norm_w_bf16) {
-                                        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(P.norm_w) + k));
+                                        const uint4 wv = *reinterpret_cast<const uint4*>(nws + (size_t)k * 2);
                                         const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
                                         for (int e = 0; e < 4; ++e) {
                                             const float2 f = __bfloat1622float2(wp[e]);
-                                            w[i][2 * e] = f.x; w[i][2 * e + 1] = f.y;
+                                            w[2 * e] = f.x; w[2 * e + 1] = f.y;
                                         }
                                     } else {
-                                        const float* wf = reinterpret_cast<const float*>(P.norm_w) + k;
-                                        const float4 wa = __ldg(reinterpret_cast<const float4*>(wf));
-                                        const float4 wb = __ldg(reinterpret_cast<const float4*>(wf + 4));
-                                        w[i][0] = wa.x; w[i][1] = wa.y; w[i][2] = wa.z; w[i][3] = wa.w;
-                                        w[i][4] = wb.x; w[i][5] = wb.y; w[i][6] = wb.z; w[i][7] = wb.w;
+                                        const float4 wa = *reinterpret_cast<const float4*>(nws + (size_t)k * 4);
+                                        const float4 wb = *reinterpret_cast<const float4*>(nws + (size_t)k * 4 + 16);
+                                        w[0] = wa.x; w[1] = wa.y; w[2] = wa.z; w[3] = wa.w; w[4] = wb.x; w[5] = wb.y; w[6] = wb.z; w[7] = wb.w;
                                     }
+                                    float x[8];
+                                    x[0] = x0.x * w[0]; x[1] = x0.y * w[1]; x[2] = x0.z * w[2]; x[3] = x0.w * w[3];
+                                    x[4] = x1.x * w[4]; x[5] = x1.y * w[5]; x[6] = x1.z * w[6]; x[7] = x1.w * w[7];
+                                    *reinterpret_cast<uint4*>(xs + (size_t)((k >> 6) - kb0) * p.x_kb_bytes + rr * 128 + (((u & 7) ^ (rr & 7)) << 4)) = pack8(x);
                                 }
                             }
-#pragma unroll
-                            for (int i = 0; i < UB; ++i) {
-                                const int u = u0 + 128 * i, k = u * 8;
-                                const bool mine = u < u_end && k >= k_lo && k < k_hi;
-                                const int kbl = (k >> 6) - kb0, c = u & 7;
-#pragma unroll
-                                for (int j = 0; j < RG; ++j) {
-                                    const float4 x0 = a[j][i], x1 = b[j][i];
-                                    ss[j] += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w
-                                           + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
-                                    const int r = r0 + j;
-                                    if (mine && r < M) {
-                                        float x[8];
-                                        x[0] = x0.x * w[i][0]; x[1] = x0.y * w[i][1]; x[2] = x0.z * w[i][2]; x[3] = x0.w * w[i][3];
-                                        x[4] = x1.x * w[i][4]; x[5] = x1.y * w[i][5]; x[6] = x1.z * w[i][6]; x[7] = x1.w * w[i][7];
-                                        *reinterpret_cast<uint4*>(xs + (size_t)kbl * (BN * BK * 2) + r * 128 + ((c ^ (r & 7)) << 4)) = pack8(x);
-                                    }
-                                }
-                            }
+                            ss = warp_sum(ss);
+                            if (lane == 0) row_scale[rr] = 1.0f / sqrtf(ss / (float)P.K + P.eps);
                         }
-                        if (!scaled) {
-#pragma unroll
-                            for (int j = 0; j < RG; ++j) {
-                                const float t = warp_sum(ss[j]);
-                                if (lane == 0 && r0 + j < M) row_part[quarter * BN + r0 + j] = t;
-                            }
-                        }
+                        // the staged rows may be overwritten, the scales are there for all warps
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        if (threadIdx.x == 64) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     }
                     // columns of the last stage that lie beyond K meet zero weights: they must not be NaN
                     for (int u = max(upr, k_lo >> 3) + te; u < (k_hi >> 3); u += 128)
                         for (int r = 0; r < M; ++r)
-                            *reinterpret_cast<uint4*>(xs + (size_t)((u >> 3) - kb0) * (BN * BK * 2) + r * 128 + (((u & 7) ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                            *reinterpret_cast<uint4*>(xs + (size_t)((u >> 3) - kb0) * p.x_kb_bytes + r * 128 + (((u & 7) ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(x_ready);
-                    if (!scaled) {
-                        // the RMS scale of every token, applied to the accumulator later
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        if (te < M)
-                            row_scale[te] = 1.0f / sqrtf((row_part[te] + row_part[BN + te] + row_part[2 * BN + te] + row_part[3 * BN + te])
-                                                         / (float)P.K + P.eps);
-                        scaled = true;
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                    }
                 }
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(x_ready);
                 // ---- the accumulator: lanes are weight rows (features), columns are tokens
-                ok = mbar_wait(acc_full, n & 1, p.error, ERR_CHAIN_EPILOGUE);
+                if (ok) ok = mbar_wait(acc_full, n & 1, p.error, ERR_CHAIN_EPILOGUE);
                 tc_fence_after();
                 const int fl = quarter * 32 + lane;
                 const int feat = fl < P.a_box ? tile * P.a_box + fl : 0x3fffffff;
-                if (ok && n_kb > 0) {
-                    for (int c0 = 0; c0 < BN && c0 < M; c0 += 16) {
-                        float v[16];
-                        tmem_ld16(taddr + c0, v);
-                        if (P.x_kind == X_NORM) {
+                for (int c0 = 0; c0 < M && ok; c0 += 4) {
+                    float v[4];
+                    tmem_ld4(taddr + c0, v);
 #pragma unroll
-                            for (int j = 0; j < 16; ++j) v[j] *= row_scale[min(c0 + j, BN - 1)];
-                        }
-                        if (P.out_kind == OUT_ADD_F32) {
-                            float* o = reinterpret_cast<float*>(P.out);
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (c0 + j < M && feat < P.N) atomicAdd(o + (size_t)(c0 + j) * P.ld_out + feat, v[j]);
-                        } else if (P.out_kind == OUT_SILU_BF16) {
-                            bf16* o = reinterpret_cast<bf16*>(P.out);
-#pragma unroll
-                            for (int j = 0; j < 16; ++j) {
-                                const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);   // even lane: gate, odd: up
-                                if (c0 + j < M && feat < P.N && (lane & 1) == 0)
-                                    o[(size_t)(c0 + j) * P.ld_out + (feat >> 1)] = __float2bfloat16_rn(silu_mul(v[j], up));
-                            }
-                        } else {
-                            bf16* o = reinterpret_cast<bf16*>(P.out);
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (c0 + j < M && feat < P.N) o[(size_t)(c0 + j) * P.ld_out + feat] = __float2bfloat16_rn(v[j]);
+                    for (int j = 0; j < 4; ++j) {
+                        const int tok = c0 + j;
+                        const float a = P.x_kind == X_NORM ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
+                        const float up = __shfl_xor_sync(0xffffffffu, a, 1);       // SiLU: even lane gate, odd lane up
+                        if (tok < M && feat < P.N) {
+                            if (P.out_kind == OUT_ADD_F32)
+                                atomicAdd(reinterpret_cast<float*>(P.out) + (size_t)tok * P.ld_out + feat, a);
+                            else if (P.out_kind == OUT_BF16)
+                                reinterpret_cast<bf16*>(P.out)[(size_t)tok * P.ld_out + feat] = __float2bfloat16_rn(a);
+                            else if ((lane & 1) == 0)
+                                reinterpret_cast<bf16*>(P.out)[(size_t)tok * P.ld_out + (feat >> 1)] = __float2bfloat16_rn(silu_mul(a, up));
                         }
                     }
                 }
@@ -469,89 +465,94 @@ int launch_chain(const Maps& maps, const Params& p, int grid, size_t smem, cudaS
 }
 }  // namespace
 
-// One product of a chain, as the caller describes it.
-struct RiChainPhase {
-    const void* w;              // bf16 [N][K], K a multiple of 8, 16-byte aligned
-    int N, K;
-    int x_kind;                 // 0: x is bf16 [M][ld_x]; 1: x is the fp32 stream [M][ld_x] and the
-    int ld_x;                   //    operand is x * norm_w * rsqrt(mean(x^2) + eps)
-    const void* x;
-    const void* norm_w;
-    int norm_w_dtype;
-    float eps;
-    int out_kind;               // 0: fp32 out += product; 1: bf16 out[M][N/2] = silu(gate) * up over
-    int ld_out;                 //    alternating weight rows; 2: bf16 out = product
-    void* out;
-};
+namespace {
+// Where everything lies in shared memory for a chain of these products and M tokens; false
+// if it does not fit.  [head | ring of weight stages | activation operand | staged rows | norm weight]
+struct Layout { int bn, x_kb_bytes, xs_bytes, stage_rows, stage_bytes, nw_bytes, stages; };
 
-struct RiChainRope {
-    float* qkv; int ld;
-    const int* positions; const float* cos_t; const float* sin_t; const int* slot_of_token;
-    void* q_out; int ld_q;
-    void* cache;
-    int Hq, Hkv, hd, rot, page_size;
-};
+bool plan_phase(const RiChainPhase& f, int sms, int* a_box, int* tiles, int* splits, int* per) {
+    if (f.N < 1 || f.K < 8 || f.K % 8) return false;
+    const int kblocks = (f.K + KSTEP - 1) / KSTEP, tiles128 = (f.N + BM - 1) / BM;
+    if (f.out_kind == OUT_ADD_F32) {
+        *a_box = BM; *tiles = tiles128;
+        const int want = max(1, min(kblocks, sms / tiles128));
+        *per = (kblocks + want - 1) / want;
+        *splits = (kblocks + *per - 1) / *per;
+    } else {
+        // cut along N only, into a whole number of waves of nearly equal tiles
+        const int waves = (tiles128 + sms - 1) / sms;
+        *a_box = min(BM, round_up((f.N + waves * sms - 1) / (waves * sms), 16));
+        *tiles = (f.N + *a_box - 1) / *a_box;
+        *splits = 1; *per = kblocks;
+    }
+    return true;
+}
 
-// Shared memory the chain would need with `M` tokens (0 if it cannot run): the caller uses
+bool plan_layout(const RiChainPhase* phases, int n_phases, int M, int sms, Layout* L) {
+    if (n_phases < 1 || n_phases > MAX_PHASES || M < 1 || M > 32 || sms < 1) return false;
+    L->bn = M <= 16 ? 16 : 32;
+    L->x_kb_bytes = M <= 8 ? 1024 : L->bn * BK * 2;           // 8 tokens: one group of 8 rows, read twice
+    L->xs_bytes = 0; L->stage_bytes = 0; L->nw_bytes = 0; L->stage_rows = 1;
+    int k_norm = 0;
+    for (int i = 0; i < n_phases; ++i) {
+        int a_box, tiles, splits, per;
+        if (!plan_phase(phases[i], sms, &a_box, &tiles, &splits, &per)) return false;
+        L->xs_bytes = max(L->xs_bytes, per * SUBS * L->x_kb_bytes);
+        if (phases[i].x_kind == X_NORM) {
+            k_norm = max(k_norm, phases[i].K);
+            L->nw_bytes = max(L->nw_bytes, round_up(phases[i].K * (phases[i].norm_w_dtype == RI_BF16 ? 2 : 4), 1024));
+        }
+    }
+    if (k_norm > 0) {
+        if (k_norm * 4 > ROW_STAGE_BYTES) return false;
+        L->stage_rows = min(M, ROW_STAGE_BYTES / (k_norm * 4));
+        L->stage_bytes = round_up(L->stage_rows * k_norm * 4, 1024);
+    }
+    const int ring = SMEM_LIMIT - 1024 - HEAD_BYTES - L->xs_bytes - L->stage_bytes - L->nw_bytes;
+    L->stages = min(MAX_STAGES, ring / STAGE_BYTES);
+    return L->stages >= 2;
+}
+}  // namespace
+
+// Whether the chain can run these products with `M` tokens (1) or not (0): the caller uses
 // this to decide between the chain and separate kernels.
 RI_API int ri_decode_chain_fits(const RiChainPhase* phases, int n_phases, int M, int sms) {
-    if (n_phases < 1 || n_phases > MAX_PHASES || M < 1 || M > 32 || sms < 1) return 0;
-    const int bn = M <= 16 ? 16 : 32;
-    int xs = 0;
-    for (int i = 0; i < n_phases; ++i) {
-        const RiChainPhase& f = phases[i];
-        if (f.N < 1 || f.K < 8 || f.K % 8) return 0;
-        const int kblocks = (f.K + KSTEP - 1) / KSTEP, tiles = (f.N + BM - 1) / BM;
-        int splits = f.out_kind == OUT_ADD_F32 ? max(1, min(kblocks, sms / tiles)) : 1;
-        const int per = (kblocks + splits - 1) / splits;
-        xs = max(xs, per * SUBS * bn * BK * 2);
-    }
-    const int ring = SMEM_LIMIT - 1024 - HEAD_BYTES - xs;
-    return ring >= 3 * STAGE_BYTES ? xs : 0;
+    Layout L;
+    return phases && plan_layout(phases, n_phases, M, sms, &L) ? 1 : 0;
 }
 
 RI_API int ri_decode_chain(const RiChainPhase* phases, int n_phases, const RiChainRope* rope, int M,
                            unsigned* grid_bar, int* error, int sms, void* stream) {
-    if (!phases || n_phases < 1 || n_phases > MAX_PHASES || M < 1 || M > 32 || !grid_bar || !error || sms < 1)
-        return (int)cudaErrorInvalidValue;
-    const int bn = M <= 16 ? 16 : 32;
+    Layout L;
+    if (!phases || !grid_bar || !error || !plan_layout(phases, n_phases, M, sms, &L)) return (int)cudaErrorInvalidValue;
     Maps maps;
     Params p = {};
     p.M = M; p.n_phases = n_phases; p.grid_bar = grid_bar; p.error = error;
-    int xs = 0;
     for (int i = 0; i < n_phases; ++i) {
         const RiChainPhase& f = phases[i];
         Phase& P = p.ph[i];
-        if (!f.w || !f.x || !f.out || f.N < 1 || f.K < 8 || f.K % 8 || (reinterpret_cast<uintptr_t>(f.w) & 15) ||
-            (reinterpret_cast<uintptr_t>(f.x) & 15) || f.out_kind < 0 || f.out_kind > 2 || f.x_kind < 0 || f.x_kind > 1)
+        if (!f.w || !f.x || !f.out || (reinterpret_cast<uintptr_t>(f.w) & 15) || (reinterpret_cast<uintptr_t>(f.x) & 15) ||
+            f.out_kind < 0 || f.out_kind > 2 || f.x_kind < 0 || f.x_kind > 1)
             return (int)cudaErrorInvalidValue;
-        if (f.x_kind == X_BF16 && f.ld_x % 8) return (int)cudaErrorInvalidValue;
+        if (f.x_kind == X_BF16 && (f.ld_x % 8 || f.x_rows < (M <= 8 ? 8 : L.bn))) return (int)cudaErrorInvalidValue;
         if (f.x_kind == X_NORM && (f.ld_x % 4 || !f.norm_w || (reinterpret_cast<uintptr_t>(f.norm_w) & 15))) return (int)cudaErrorInvalidValue;
         if (f.out_kind == OUT_SILU_BF16 && f.N % 2) return (int)cudaErrorInvalidValue;
-        const int kblocks = (f.K + KSTEP - 1) / KSTEP, tiles128 = (f.N + BM - 1) / BM;
         P.N = f.N; P.K = f.K;
-        if (f.out_kind == OUT_ADD_F32) {
-            P.a_box = BM; P.tiles = tiles128;
-            const int splits = max(1, min(kblocks, sms / tiles128));
-            P.per = (kblocks + splits - 1) / splits;
-            P.splits = (kblocks + P.per - 1) / P.per;
-        } else {
-            // cut along N only, into a whole number of waves of nearly equal tiles
-            const int waves = (tiles128 + sms - 1) / sms;
-            P.a_box = min(BM, round_up((f.N + waves * sms - 1) / (waves * sms), 16));
-            P.tiles = (f.N + P.a_box - 1) / P.a_box;
-            P.splits = 1; P.per = kblocks;
-        }
+        plan_phase(f, sms, &P.a_box, &P.tiles, &P.splits, &P.per);
         P.x_kind = f.x_kind; P.ld_x = f.ld_x; P.x = f.x; P.norm_w = f.norm_w;
         P.norm_w_bf16 = f.norm_w_dtype == RI_BF16 ? 1 : 0; P.eps = f.eps;
         P.out_kind = f.out_kind; P.ld_out = f.ld_out; P.out = f.out;
-        xs = max(xs, P.per * SUBS * bn * BK * 2);
         RI_CHECKED(ri_tc_weight_map(f.w, f.N, f.K, P.a_box, &maps.m[i]));
+        // a bf16 activation matrix is fetched by TMA, a block of 64 columns of the first rows at a time
+        if (f.x_kind == X_BF16) RI_CHECKED(ri_tc_weight_map(f.x, f.x_rows, f.K, M <= 8 ? 8 : L.bn, &maps.x[i]));
+        else maps.x[i] = maps.m[i];
     }
-    const int ring = SMEM_LIMIT - 1024 - HEAD_BYTES - xs;
-    if (ring < 3 * STAGE_BYTES) return (int)cudaErrorInvalidValue;
-    p.stages = min(MAX_STAGES, ring / STAGE_BYTES);
+    p.stages = L.stages;
+    p.x_kb_bytes = L.x_kb_bytes;
     p.xs_off = HEAD_BYTES + p.stages * STAGE_BYTES;
+    p.stage_off = p.xs_off + L.xs_bytes;
+    p.stage_rows = L.stage_rows;
+    p.nw_off = p.stage_off + L.stage_bytes;
     if (rope) {
         Rope& R = p.rope;
         R.enabled = 1; R.qkv = rope->qkv; R.ld = rope->ld; R.positions = rope->positions; R.cos_t = rope->cos_t;
@@ -561,7 +562,7 @@ RI_API int ri_decode_chain(const RiChainPhase* phases, int n_phases, const RiCha
         if (!R.qkv || !R.positions || !R.cos_t || !R.sin_t || !R.q_out || R.rot > R.hd || R.rot % 2 || R.page_size < 1)
             return (int)cudaErrorInvalidValue;
     }
-    const size_t smem = 1024 + (size_t)p.xs_off + xs;
+    const size_t smem = 1024 + (size_t)p.nw_off + L.nw_bytes;
     cudaStream_t s = (cudaStream_t)stream;
-    return bn == 16 ? launch_chain<16>(maps, p, sms, smem, s) : launch_chain<32>(maps, p, sms, smem, s);
+    return L.bn == 16 ? launch_chain<16>(maps, p, sms, smem, s) : launch_chain<32>(maps, p, sms, smem, s);
 }

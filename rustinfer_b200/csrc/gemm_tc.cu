@@ -194,44 +194,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
         pdl_wait();
+        // Stages are given back in pairs (the MMA thread commits once per two k-blocks, which
+        // halves its fixed cost per k-block), so the producer asks for a pair when it reaches
+        // the even stage and then fills both.
         bool ok = true;
-        int it = 0;                                       // k-blocks loaded so far, over all tiles
+        int it = 0, s = 0;                                // k-blocks loaded so far, over all tiles; ring position
+        unsigned par = 1;                                 // parity of the release this round waits for
         for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
             const int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
             const int w0 = p.swap ? a0 : b0, x0 = p.swap ? b0 : a0;
             for (int i = 0; i < n_kb; ++i, ++it) {
-                const int s = it % STAGES, round = it / STAGES;
                 unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                 if (it >= pre) {
-                    if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, p.error, ERR_PRODUCER_WAIT)) { ok = false; break; }
+                    if (it >= STAGES && (s & 1) == 0 &&
+                        !mbar_try_wait(&empty[s >> 1], par) && !mbar_wait(&empty[s >> 1], par, p.error, ERR_PRODUCER_WAIT)) { ok = false; break; }
                     mbar_expect_tx(&full[s], stage_tx);
                     tma_load_2d(st + woff, wmap, &full[s], (kb_begin + i) * BK, w0);
                 }
                 tma_load_2d(st + xoff, xmap, &full[s], (kb_begin + i) * BK, x0);
+                if (++s == STAGES) { s = 0; par ^= 1u; }
             }
         }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
         // instruction descriptor: D fp32, A and B bf16, both K-major, N = BN, M = 128
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+        // One scalar thread feeds the tensor core, and its own instruction stream is what
+        // limits the rate (measured: a wait, four MMAs and a commit with descriptors rebuilt
+        // and the ring position divided out cost 870 cycles a k-block against 512 of tensor
+        // work at N = 256).  So: descriptors are made once and stepped by adds, the ring
+        // position is counted, the wait tries once before it loops, and one commit frees two
+        // stages.
+        const uint64_t desc0 = smem_desc(smem_u32(tiles));
+        const unsigned stage_step = (unsigned)STAGE_BYTES >> 4, b_step = (unsigned)(p.a_box * BK * 2) >> 4;
         bool ok = true;
-        int it = 0, t = 0;
+        int s = 0, t = 0;
+        unsigned par = 0;
         for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x, ++t) {
             const int buf = t & 1, use = t >> 1;
             // the epilogue has emptied this accumulator (first use of a buffer passes at once)
             if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
             tc_fence_after();
             const unsigned tmem_d = tmem_base + buf * C::ACC_COLS;
-            for (int i = 0; i < n_kb; ++i, ++it) {
-                const int s = it % STAGES, round = it / STAGES;
-                if (!mbar_wait(&full[s], round & 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
+            for (int i = 0; i < n_kb; ++i) {
+                if (!mbar_try_wait(&full[s], par) && !mbar_wait(&full[s], par, p.error, ERR_MMA_WAIT)) { ok = false; break; }
                 tc_fence_after();
-                const unsigned sa = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                const unsigned sb = sa + p.a_box * BK * 2;
+                const uint64_t da = desc0 + (uint64_t)(s * stage_step), db = da + (uint64_t)b_step;
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)
-                    mma_bf16_ss(tmem_d, smem_desc(sa + k * 32), smem_desc(sb + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
-                tc_commit(&empty[s]);                     // the stage is free once these MMAs have read it
+                    mma_bf16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                if (s & 1) tc_commit(&empty[s >> 1]);     // the pair is free once these MMAs have read it
+                if (++s == STAGES) { s = 0; par ^= 1u; }
             }
             tc_commit(&acc_full[buf]);                    // the accumulator is complete
         }
@@ -475,6 +488,8 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     p.budget = (swap && bn <= 64) ? g_stream_budget : SMEM_BUDGET;
     p.stages = p.budget / p.stage_bytes;
     if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+    p.stages &= ~1;                                       // stages are released in pairs
+    if (p.stages < 2) return (int)cudaErrorInvalidValue;
     p.tiles_a = (p.a_rows + a_box - 1) / a_box;
     p.n_tiles = p.tiles_a * tiles_b;
     int st = make_map(A, p.a_rows, K, a_box, &ma);

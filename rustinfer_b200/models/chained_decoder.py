@@ -135,10 +135,11 @@ class ChainedDecoder:
             a, f = block.mixer, block.ffn
             attn = self._buffer("attn", a.Hq * a.hd, torch.bfloat16)
             mid = self._buffer("mid", f.inter, torch.bfloat16)
-            products = [K.ChainProduct(a.o.weight, attn[:T], self.h[:T], K.CHAIN_ADD_F32),
+            rows = K.CHAIN_MAX_TOKENS
+            products = [K.ChainProduct(a.o.weight, attn[:T], self.h[:T], K.CHAIN_ADD_F32, x_rows=rows),
                         K.ChainProduct(f.gate_up.weight, self.h[:T], mid[:T], K.CHAIN_SILU_BF16,
                                        norm=(self.norm_w[id(block.ffn_norm)], block.ffn_norm.eps)),
-                        K.ChainProduct(f.down.weight, mid[:T], self.h[:T], K.CHAIN_ADD_F32)]
+                        K.ChainProduct(f.down.weight, mid[:T], self.h[:T], K.CHAIN_ADD_F32, x_rows=rows)]
             rope = None
             if i + 1 < len(self.entries):
                 nxt = self.entries[i + 1][0]

@@ -210,7 +210,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
 
 class _ChainPhase(ctypes.Structure):
     _fields_ = [("w", ctypes.c_void_p), ("N", ctypes.c_int), ("K", ctypes.c_int), ("x_kind", ctypes.c_int),
-                ("ld_x", ctypes.c_int), ("x", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
+                ("ld_x", ctypes.c_int), ("x_rows", ctypes.c_int), ("x", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
                 ("norm_w_dtype", ctypes.c_int), ("eps", ctypes.c_float), ("out_kind", ctypes.c_int),
                 ("ld_out", ctypes.c_int), ("out", ctypes.c_void_p)]
 
@@ -234,8 +234,11 @@ class ChainProduct:
     silu(gate) * up of a weight whose rows alternate gate_j, up_j into bf16 [M, N/2];
     CHAIN_BF16 stores bf16 [M, N]."""
 
-    def __init__(self, w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, out_kind: int, norm=None):
+    def __init__(self, w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, out_kind: int, norm=None,
+                 x_rows: Optional[int] = None):
         self.w, self.x, self.out, self.out_kind, self.norm = w, x, out, out_kind, norm
+        # rows behind x that may be read (not used): a bf16 x is fetched in boxes of 8, 16 or 32 rows
+        self.x_rows = x.shape[0] if x_rows is None else x_rows
         N, Kd = w.shape
         want_x = torch.float32 if norm is not None else torch.bfloat16
         cols = N // 2 if out_kind == CHAIN_SILU_BF16 else N
@@ -249,6 +252,7 @@ class ChainProduct:
     def fill(self, c: "_ChainPhase") -> None:
         c.w, c.N, c.K = self.w.data_ptr(), self.w.shape[0], self.w.shape[1]
         c.x, c.ld_x, c.x_kind = self.x.data_ptr(), self.x.stride(0), 1 if self.norm is not None else 0
+        c.x_rows = self.x_rows
         if self.norm is not None:
             c.norm_w, c.norm_w_dtype, c.eps = self.norm[0].data_ptr(), dtype_code(self.norm[0].dtype), float(self.norm[1])
         else:
