@@ -116,13 +116,14 @@ __device__ __forceinline__ void store_row16(const Params& p, int tok, int feat0,
             break;
         }
         case EPI_RESIDUAL: {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + row + feat0);
+            // a reduction at the memory side instead of load, add, store: nothing comes back, so
+            // the thread does not sit out a trip to L2 per 16 columns (each element is added
+            // once, so the result does not depend on any order)
+            float* dst = reinterpret_cast<float*>(p.out) + row + feat0;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float4 h = dst[j];
-                h.x += v[4 * j]; h.y += v[4 * j + 1]; h.z += v[4 * j + 2]; h.w += v[4 * j + 3];
-                dst[j] = h;
-            }
+            for (int j = 0; j < 4; ++j)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                             ::"l"(dst + 4 * j), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
             break;
         }
         case EPI_SILU: {
