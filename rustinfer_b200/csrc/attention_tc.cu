@@ -221,28 +221,52 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap cache_map, const Params 
         // ------------------------------------------------------------------ TMA producer
         pdl_wait();                                            // the cache was written by the kernel before
         const int* bt = p.block_table + (size_t)b * p.table_stride;
-        const int boxes = BN / p.box_rows;
+        const int boxes = BN / p.box_rows;                     // at most 8 pages meet a tile
         bool ok = true;
+        // This one thread sets the pace of the CTA, so it does no division and waits for no
+        // look-up: pages are smaller than a tile (a box per page, from its first key) or whole
+        // multiples of it (one box, block and offset counted along), and the page numbers of
+        // a tile are read from the block table one tile ahead, all at once.  (Eight look-ups
+        // and sixteen divisions in a row before the boxes of a tile went out took 1.5 us and
+        // were the period of the whole kernel.)
+        // Pages past the request's last one are never allocated: its first page is read instead
+        // (those keys are masked, and their V rows are zeroed before use).
+        const bool small_pages = p.page_size < BN;
+        int blk = (t_begin * BN) / p.page_size, off = small_pages ? 0 : (t_begin * BN) % p.page_size;
+        int pages[8], pages_next[8];
+        auto look_up = [&](int key0, int blk0, bool live, int (&out)[8]) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                out[c] = (live && c < boxes) ? bt[key0 + c * p.box_rows < kvl ? blk0 + c : 0] : 0;
+        };
+        look_up(t_begin * BN, blk, n_tiles > 0, pages);
+        const int kv_step = p.Hkv * p.page_size;               // rows between a page's keys and its values
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int s = j % NS, u = j / NS;
             const int key0 = (t_begin + j) * BN;
+            int blk_n = blk, off_n = off;
+            if (small_pages) blk_n += boxes;
+            else if ((off_n += BN) >= p.page_size) { off_n = 0; ++blk_n; }
+            look_up(key0 + BN, blk_n, j + 1 < n_tiles, pages_next);
             for (int kv = 0; kv < 2 && ok; ++kv) {
                 uint64_t* full = kv ? &v_full[s] : &k_full[s];
                 uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
                 if (u > 0 && !mbar_wait(empty, (u - 1) & 1, p.error, ERR_PRODUCER)) { ok = false; break; }
                 unsigned char* dst = sm + (kv ? OFF_V : OFF_K) + s * KV_STAGE;
                 mbar_expect_tx(full, KV_STAGE);
-                for (int c = 0; c < boxes; ++c) {
-                    const int key = key0 + c * p.box_rows;
-                    // pages past the request's last one are never allocated: read its first page
-                    // instead (those keys are masked, and their V rows are zeroed before use)
-                    const int blk = key < kvl ? key / p.page_size : 0;
-                    const int page = bt[blk];
-                    const int row = ((page * 2 + kv) * p.Hkv + g) * p.page_size + (key < kvl ? key % p.page_size : 0);
-                    for (int kb = 0; kb < KB; ++kb)
-                        tma_load_2d(dst + kb * (BN * 128) + c * p.box_rows * 128, &cache_map, full, kb * 64, row);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    if (c < boxes) {
+                        const int row = (pages[c] * 2 * p.Hkv + g) * p.page_size + kv * kv_step +
+                                        (key0 + c * p.box_rows < kvl ? off : 0);
+                        for (int kb = 0; kb < KB; ++kb)
+                            tma_load_2d(dst + kb * (BN * 128) + c * p.box_rows * 128, &cache_map, full, kb * 64, row);
+                    }
                 }
             }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) pages[c] = pages_next[c];
+            blk = blk_n; off = off_n;
         }
     } else if (warp == 1 && lane == 0) {
         // -------------------------------------------------------------------- MMA issuer

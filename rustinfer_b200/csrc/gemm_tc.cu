@@ -44,6 +44,7 @@ constexpr int MAX_STAGES = 32;
 // shared memory, so that the next product's CTAs can move in and prefetch beside them
 constexpr int SMEM_BUDGET = 200 * 1024;
 constexpr int SMEM_BUDGET_STREAM = 96 * 1024;
+constexpr int SMEM_BUDGET_LONG = 160 * 1024;
 int g_stream_budget = SMEM_BUDGET_STREAM;
 // The MMA always reads 128 rows of A; when a tile loads fewer, the rows past them are
 // whatever follows in shared memory, and the lanes they feed are never stored.  The slack
@@ -487,6 +488,11 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     p.a_box = a_box;
     p.stage_bytes = (a_box + bn) * BK * 2;
     p.budget = (swap && bn <= 64) ? g_stream_budget : SMEM_BUDGET;
+    // a long weight stream per CTA (the head over a large vocabulary) is worth a deeper ring than
+    // the half-SM one that lets the next product move in early: 525 MB at batch 8 took 98 us with
+    // 96 KB and 85.7 us (6.1 TB/s) with 160 KB
+    if (swap && bn <= 64 && g_stream_budget < SMEM_BUDGET_LONG &&
+        (double)p.a_rows * K * 2 / 148.0 > 1048576.0) p.budget = SMEM_BUDGET_LONG;
     p.stages = p.budget / p.stage_bytes;
     if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
     p.stages &= ~1;                                       // stages are released in pairs
