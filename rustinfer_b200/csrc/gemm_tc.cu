@@ -26,6 +26,7 @@
 #include "common.cuh"
 #include "tc_primitives.cuh"
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -412,6 +413,190 @@ int make_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out
     return 0;
 }
 
+
+// ------------------------------------------------------------ a 256 x 256 tile on a CTA pair
+// Many tokens (prefill): what limits the one-CTA kernel is operand traffic, 48 KB from L2 per
+// 128 x 256 x 64 block and SM.  Here two CTAs of a cluster share a 256 x 256 tile: each loads
+// its own 128 rows of activations and HALF of the 256 weight rows (32 KB per block), and one
+// thread of the even CTA issues tcgen05.mma.cta_group::2, which reads A from each CTA's own
+// shared memory, the two halves of B from both, and writes each CTA's 128 x 256 accumulator into
+// its own tensor memory.  Barriers: TMA copies of both CTAs complete on the even CTA's `full`
+// (its address with the peer bit cleared); tcgen05.commit with a two-CTA multicast frees the
+// stages and publishes the accumulator in both; the odd CTA's epilogue warps arrive on the even
+// CTA's `acc_empty` through its cluster address.  Every wait on an mbarrier is bounded.
+constexpr int PAIR_BN = 256;
+constexpr unsigned PEER_BIT_MASK = 0xFEFFFFFFu;          // shared::cluster address of the even CTA's copy
+
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar) & PEER_BIT_MASK), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void mma_bf16_ss_pair(unsigned tmem_d, uint64_t a, uint64_t b, unsigned idesc, unsigned accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
+}
+// arrive on the barrier at the same offset in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, unsigned rank) {
+    asm volatile("{\n\t.reg .b32 ra;\n\t"
+                 "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+                 "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+                 ::"r"(smem_u32(bar)), "r"(rank) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const Params p) {
+    constexpr int BN = PAIR_BN, ACC_COLS = 256, TMEM_COLS = 512;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int STAGES = p.stages, STAGE_BYTES = p.stage_bytes;       // A 128 x 64 and half of B, 128 x 64: 32 KB
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.budget + SMEM_TAIL);
+    uint64_t* empty = full + MAX_STAGES;
+    uint64_t* acc_full = empty + MAX_STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int n_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                    // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        const unsigned pair_tx = 2u * (unsigned)STAGE_BYTES;          // both CTAs' copies land on the even CTA's barrier
+        pdl_trigger();
+        pdl_wait();
+        bool ok = true;
+        int it = 0, s = 0;
+        unsigned par = 1;
+        for (int tile = pair; tile < p.n_tiles && ok; tile += pairs) {
+            const int a0 = (tile % p.tiles_a) * 256 + (int)rank * BM, b0 = (tile / p.tiles_a) * BN + (int)rank * BM;
+            for (int i = 0; i < n_kb; ++i, ++it) {
+                unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                if (it >= STAGES && (s & 1) == 0 &&
+                    !mbar_try_wait(&empty[s >> 1], par) && !mbar_wait(&empty[s >> 1], par, p.error, ERR_PRODUCER_WAIT)) { ok = false; break; }
+                if (rank == 0) mbar_expect_tx(&full[s], pair_tx);
+                tma_load_2d_pair(st, &map_a, &full[s], i * BK, a0);
+                tma_load_2d_pair(st + BM * BK * 2, &map_b, &full[s], i * BK, b0);
+                if (++s == STAGES) { s = 0; par ^= 1u; }
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ------------------------------------------------------------ MMA issuer (even CTA only)
+        // D fp32, A and B bf16, both K-major, N = 256, M = 256 over the two CTAs
+        const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
+        const uint64_t desc0 = smem_desc(smem_u32(tiles));
+        const unsigned stage_step = (unsigned)STAGE_BYTES >> 4, b_step = (unsigned)(BM * BK * 2) >> 4;
+        bool ok = true;
+        int s = 0, t = 0;
+        unsigned par = 0;
+        for (int tile = pair; tile < p.n_tiles && ok; tile += pairs, ++t) {
+            const int buf = t & 1, use = t >> 1;
+            if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
+            tc_fence_after();
+            const unsigned tmem_d = tmem_base + buf * ACC_COLS;
+            for (int i = 0; i < n_kb; ++i) {
+                if (!mbar_try_wait(&full[s], par) && !mbar_wait(&full[s], par, p.error, ERR_MMA_WAIT)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t da = desc0 + (uint64_t)(s * stage_step), db = da + (uint64_t)b_step;
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    mma_bf16_ss_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                if (s & 1) tc_commit_pair(&empty[s >> 1]);
+                if (++s == STAGES) { s = 0; par ^= 1u; }
+            }
+            tc_commit_pair(&acc_full[buf]);
+        }
+        if (!ok) {
+            for (int st = 0; st < STAGES; ++st)
+                for (int q = 0; q < 2; ++q)
+                    if (mbar_try_wait(&full[st], q)) break;
+            for (unsigned spin = 0; spin < 4096; ++spin) __nanosleep(256);
+        }
+    } else if (warp >= 2) {
+        // -------------------------------------------------------------------- epilogue (both CTAs)
+        const int quarter = warp & 3;
+        bool ok = true;
+        int t = 0;
+        pdl_wait();
+        for (int tile = pair; tile < p.n_tiles; tile += pairs, ++t) {
+            const int a0 = (tile % p.tiles_a) * 256 + (int)rank * BM, b0 = (tile / p.tiles_a) * BN;
+            const int ra = a0 + quarter * 32 + lane;
+            const int buf = t & 1, use = t >> 1;
+            if (ok) ok = mbar_wait(&acc_full[buf], use & 1, p.error, ERR_EPILOGUE_WAIT);
+            tc_fence_after();
+            const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + buf * ACC_COLS;
+            if (ok) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr + c0, v);
+                    store_row16(p, ra, b0 + c0, v);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(&acc_empty[buf], 0);      // the even CTA's MMA thread counts all eight warps
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                    // neither CTA leaves while the other may still touch it
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)TMEM_COLS) : "memory");
+    }
+}
+
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const int pairs = p.n_tiles < sms / 2 ? p.n_tiles : sms / 2;
+    RI_CHECKED(ri_launch(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(THREADS), (size_t)p.budget + SMEM_EXTRA, s, ma, mb, p));
+    return ri_launch_status();
+}
 }  // namespace
 
 int ri_tc_weight_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
@@ -499,6 +684,20 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     if (p.stages < 2) return (int)cudaErrorInvalidValue;
     p.tiles_a = (p.a_rows + a_box - 1) / a_box;
     p.n_tiles = p.tiles_a * tiles_b;
+    // many tokens: a 256 x 256 tile on a CTA pair (less operand traffic per flop)
+    static const bool pair_off = getenv("RUSTINFER_B200_GEMM_PAIR") && atoi(getenv("RUSTINFER_B200_GEMM_PAIR")) == 0;
+    if (!swap && bn == PAIR_BN && splits == 1 && a_box == BM && !pair_off && p.a_rows >= 512) {
+        p.stage_bytes = 2 * BM * BK * 2;
+        p.stages = (p.budget / p.stage_bytes) & ~1;
+        if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
+        p.tiles_a = (p.a_rows + 255) / 256;
+        p.n_tiles = p.tiles_a * ((p.b_rows + PAIR_BN - 1) / PAIR_BN);
+        int stp = make_map(A, p.a_rows, K, BM, &ma);
+        if (stp != 0) return stp;
+        stp = make_map(B, p.b_rows, K, BM, &mb);
+        if (stp != 0) return stp;
+        return launch_pair(ma, mb, p, (cudaStream_t)stream);
+    }
     int st = make_map(A, p.a_rows, K, a_box, &ma);
     if (st != 0) return st;
     st = make_map(B, p.b_rows, K, bn, &mb);
