@@ -21,6 +21,11 @@
 // Cache layout of one layer: [page][K|V][kv head][slot in page][head_dim], so a page's
 // keys of one head are one contiguous run.
 #include "common.cuh"
+#include <cuda.h>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
 
 #ifndef RI_HEAD_DIM
 #error "compile with -DRI_HEAD_DIM=<head size>"
@@ -464,6 +469,294 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
     }
 }
 
+#if RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128
+// ============================================================ decode, keys and values by TMA
+// The same arithmetic as decode_kernel (a warp takes 16 keys of every 64-key tile, mma.sync,
+// fp32 online softmax, the warps' states merged at the end), but no thread computes an address
+// in the cache: a fifth warp's one thread issues a TMA box per page and kv head into a ring of
+// 128-byte-swizzled stages (full/empty mbarriers), and the warps read them with ldmatrix
+// through the swizzle.  The cp.async kernel above spends its issue slots on page look-ups and
+// address arithmetic (3.4 TB/s at batch 8, 4.5 at batch 64); this one is bound by the ring.
+// Head sizes 64 and 128, pages of 8, 16, 32 or a multiple of 64 keys.
+constexpr int TSTAGES = 3;
+constexpr int TKB = HD / 64;                                   // 64-column blocks of a head
+constexpr int T_TILE_BYTES = DKT * 128 * TKB;                  // K (or V) of one tile
+constexpr int T_STAGE_BYTES = 2 * T_TILE_BYTES;
+constexpr int TTHREADS = DTHREADS + 32;
+constexpr unsigned T_SPIN_LIMIT = 1u << 20;
+constexpr size_t DECODE_TMA_SMEM = 1024 /*alignment*/ + (size_t)TSTAGES * T_STAGE_BYTES + 16 * (size_t)ROW * sizeof(bf16) + 256;
+static_assert((size_t)TSTAGES * T_STAGE_BYTES >= (DWARPS * 16 * (size_t)HD + 2 * DWARPS * 16) * sizeof(float), "the merge reuses the ring");
+
+__device__ __forceinline__ unsigned tsm(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tsm(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tsm(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tsm(bar)) : "memory");
+}
+__device__ __forceinline__ bool tbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(tsm(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded: false after T_SPIN_LIMIT tries, with 21 in *error
+__device__ __forceinline__ bool tbar_wait(uint64_t* bar, unsigned parity, int* error) {
+    for (unsigned i = 0; i < T_SPIN_LIMIT; ++i) {
+        if (tbar_try_wait(bar, parity)) return true;
+        if (i > 1024) __nanosleep(64);
+    }
+    atomicExch(error, 21);
+    return false;
+}
+__device__ __forceinline__ void t_tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(tsm(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(tsm(bar)), "r"(x), "r"(y) : "memory");
+}
+// where the 16 bytes of columns col..col+7 of key row `row` lie in a tile [TKB][DKT rows][128 B]
+// written by TMA with the 128-byte swizzle
+__device__ __forceinline__ const unsigned char* swz(const unsigned char* tile, int row, int col) {
+    return tile + (col >> 6) * (DKT * 128) + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(TTHREADS)
+decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __restrict__ q, int q_stride,
+                  bf16* __restrict__ out, int out_stride, const int* __restrict__ block_table, int table_stride,
+                  const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                  const int* __restrict__ entry_list, int Hq, int Hkv, int Gc, int chunks, int page_size, int box_rows,
+                  float scale_log2, int window, int splits, float* __restrict__ part_o,
+                  float* __restrict__ part_lse, int* __restrict__ error) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    bf16* Qs = reinterpret_cast<bf16*>(ring + (size_t)TSTAGES * T_STAGE_BYTES);    // [16][ROW]
+    uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(Qs) + 16 * ROW * sizeof(bf16));
+    uint64_t* empty = full + TSTAGES;
+
+    const int slot = blockIdx.z;
+    const int b = entry_list ? entry_list[slot] : slot;
+    if (b < 0) return;
+    const int split = blockIdx.y;
+    const int G = Hq / Hkv;
+    const int kvh = blockIdx.x / chunks, hc = blockIdx.x - kvh * chunks;
+    const int head0 = kvh * G + hc * Gc;
+    const int nheads = min(Gc, G - hc * Gc);
+    const int tok = cu_q[b + 1] - 1;
+    const int kvl = kv_len[b];
+    const int lo = window > 0 ? max(0, kvl - window) : 0;
+    const int t_first = lo / DKT, t_count = (kvl + DKT - 1) / DKT - t_first;
+    const int per = (t_count + splits - 1) / splits;
+    const int t_begin = t_first + split * per, t_end = min(t_begin + per, t_first + t_count);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int s = 0; s < TSTAGES; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], DWARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < DTHREADS) {
+        for (int c = tid; c < 16 * CH; c += DTHREADS) {
+            const int r = c / CH, ch = c - r * CH;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < nheads)
+                v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(head0 + r) * HD + ch * 8);
+            *reinterpret_cast<uint4*>(Qs + r * ROW + ch * 8) = v;
+        }
+    }
+    __syncthreads();
+
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    if (warp == DWARPS) {
+        // ------------------------------------------------------------------ TMA producer
+        // Lean on purpose (this thread paces the CTA): no division in the loop, page numbers
+        // read one tile ahead.  Pages past the request's last one are never allocated: its
+        // first page is read instead (those keys are masked, their V rows zeroed before use).
+        if (lane == 0) {
+            const int* bt = block_table + (size_t)b * table_stride;
+            const int boxes = DKT / box_rows;                  // at most 8 pages meet a tile
+            const bool small_pages = page_size < DKT;
+            int blk = (t_begin * DKT) / page_size, off = small_pages ? 0 : (t_begin * DKT) % page_size;
+            int pages[8], pages_next[8];
+            auto look_up = [&](int key0, int blk0, bool live, int (&dst)[8]) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    dst[c] = (live && c < boxes) ? bt[key0 + c * box_rows < kvl ? blk0 + c : 0] : 0;
+            };
+            look_up(t_begin * DKT, blk, t_begin < t_end, pages);
+            const int kv_step = Hkv * page_size;
+            bool ok = true;
+            int s = 0;
+            unsigned par = 1;
+            for (int t = t_begin; t < t_end && ok; ++t) {
+                const int key0 = t * DKT;
+                int blk_n = blk, off_n = off;
+                if (small_pages) blk_n += boxes;
+                else if ((off_n += DKT) >= page_size) { off_n = 0; ++blk_n; }
+                look_up(key0 + DKT, blk_n, t + 1 < t_end, pages_next);
+                if (t - t_begin >= TSTAGES && !tbar_try_wait(&empty[s], par) && !tbar_wait(&empty[s], par, error)) { ok = false; break; }
+                unsigned char* dst = ring + (size_t)s * T_STAGE_BYTES;
+                tbar_expect_tx(&full[s], T_STAGE_BYTES);
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        if (c < boxes) {
+                            const int row = (pages[c] * 2 * Hkv + kvh) * page_size + kv * kv_step + (key0 + c * box_rows < kvl ? off : 0);
+#pragma unroll
+                            for (int kb = 0; kb < TKB; ++kb)
+                                t_tma_load_2d(dst + kv * T_TILE_BYTES + kb * (DKT * 128) + c * box_rows * 128, &cache_map, &full[s], kb * 64, row);
+                        }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) pages[c] = pages_next[c];
+                blk = blk_n; off = off_n;
+                if (++s == TSTAGES) { s = 0; par ^= 1u; }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------------- the warps
+        unsigned qf[KS][4];
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+            ldmatrix_x4(qf[ks], Qs + (lane & 15) * ROW + ks * 16 + (lane >> 4) * 8);
+        const int kw0 = warp * 16;
+        bool ok = true;
+        int s = 0;
+        unsigned par = 0;
+        for (int t = t_begin; t < t_end && ok; ++t) {
+            const unsigned char* Kt = ring + (size_t)s * T_STAGE_BYTES;
+            unsigned char* Vt = ring + (size_t)s * T_STAGE_BYTES + T_TILE_BYTES;
+            if (!tbar_try_wait(&full[s], par) && !tbar_wait(&full[s], par, error)) { ok = false; break; }
+            if (t * DKT + kw0 < kvl) {
+                // value rows of keys past the end hold whatever the cache holds there: they meet
+                // probability zero, but zero times NaN is NaN, so they are cleared
+                if (t * DKT + kw0 + 16 > kvl) {
+                    for (int i = lane; i < 16 * TKB * 8; i += 32) {
+                        const int r = kw0 + (i / (TKB * 8)), c8 = i % (TKB * 8);
+                        if (t * DKT + r >= kvl)
+                            *reinterpret_cast<uint4*>(const_cast<unsigned char*>(swz(Vt, r, c8 * 8))) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    __syncwarp();
+                }
+                float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    unsigned kf[4];
+                    ldmatrix_x4(kf, swz(Kt, kw0 + (lane & 7) + (lane >> 4) * 8, ks * 16 + ((lane >> 3) & 1) * 8));
+                    mma_bf16(sc[0], qf[ks], kf[0], kf[1]);
+                    mma_bf16(sc[1], qf[ks], kf[2], kf[3]);
+                }
+                const int key0 = t * DKT + kw0 + (lane & 3) * 2;
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + n * 8 + (e & 1);
+                        sc[n][e] = (key >= lo && key < kvl) ? sc[n][e] * scale_log2 : -INFINITY;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], sc[n][e]);
+                    }
+                float alpha[2], muse[2];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                    mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+                    const float mnew = fmaxf(m[i], mx[i]);
+                    muse[i] = mnew == -INFINITY ? 0.f : mnew;
+                    alpha[i] = exp2f(m[i] - muse[i]);
+                    m[i] = mnew;
+                    l[i] *= alpha[i];
+                }
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    o[n][0] *= alpha[0]; o[n][1] *= alpha[0];
+                    o[n][2] *= alpha[1]; o[n][3] *= alpha[1];
+                }
+#pragma unroll
+                for (int n = 0; n < 2; ++n)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        sc[n][e] = exp2f(sc[n][e] - muse[e >> 1]);
+                        l[e >> 1] += sc[n][e];
+                    }
+                unsigned pa[4];
+                pa[0] = pack_bf16(sc[0][0], sc[0][1]);
+                pa[1] = pack_bf16(sc[0][2], sc[0][3]);
+                pa[2] = pack_bf16(sc[1][0], sc[1][1]);
+                pa[3] = pack_bf16(sc[1][2], sc[1][3]);
+#pragma unroll
+                for (int np = 0; np < NT / 2; ++np) {
+                    unsigned vf[4];
+                    ldmatrix_x4_trans(vf, swz(Vt, kw0 + (lane & 15), np * 16 + (lane >> 4) * 8));
+                    mma_bf16(o[2 * np], pa, vf[0], vf[1]);
+                    mma_bf16(o[2 * np + 1], pa, vf[2], vf[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) tbar_arrive(&empty[s]);             // this warp is done with the stage
+            if (++s == TSTAGES) { s = 0; par ^= 1u; }
+        }
+    }
+    __syncthreads();                                           // every stage is consumed, no copy is in flight
+
+    // merge the warps' states through shared memory (the ring is free now)
+    float* Os = reinterpret_cast<float*>(ring);                // [DWARPS][16][HD]
+    float* Ms = Os + DWARPS * 16 * HD;                         // [DWARPS][16]
+    float* Ls = Ms + DWARPS * 16;                              // [DWARPS][16]
+    if (warp < DWARPS) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+            l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+            const int r = (lane >> 2) + 8 * i;
+            float* orow = Os + ((size_t)warp * 16 + r) * HD + (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                orow[n * 8] = o[n][2 * i];
+                orow[n * 8 + 1] = o[n][2 * i + 1];
+            }
+            if ((lane & 3) == 0) {
+                Ms[warp * 16 + r] = m[i];
+                Ls[warp * 16 + r] = l[i];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nheads * HD; idx += TTHREADS) {
+        const int r = idx / HD, d = idx - r * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DWARPS; ++w) M = fmaxf(M, Ms[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < DWARPS; ++w) {
+                const float f = exp2f(Ms[w * 16 + r] - M);
+                L += Ls[w * 16 + r] * f;
+                O += Os[((size_t)w * 16 + r) * HD + d] * f;
+            }
+        }
+        const int head = head0 + r;
+        const float val = L > 0.f ? O / L : 0.f;
+        if (splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(val);
+        } else {
+            const size_t p = ((size_t)slot * Hq + head) * splits + split;
+            part_o[p * HD + d] = val;
+            if (d == 0) part_lse[p] = L > 0.f ? M + log2f(L) : -INFINITY;
+        }
+    }
+}
+#endif
+
 // out[token, head, :] = sum_s w_s * part_o[s] / sum_s w_s, w_s = 2^(lse_s - max lse)
 __global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                bf16* __restrict__ out, int out_stride, const int* __restrict__ cu_q,
@@ -496,6 +789,56 @@ constexpr size_t DECODE_SMEM_MERGE = (DWARPS * 16 * (size_t)HD + 2 * DWARPS * 16
 constexpr size_t DECODE_SMEM = 16 * (size_t)ROW * sizeof(bf16) +
                                (DECODE_SMEM_KV > DECODE_SMEM_MERGE ? DECODE_SMEM_KV : DECODE_SMEM_MERGE);
 
+#if RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+struct TMapKey {
+    const void* ptr; long long rows; int box_rows;
+    bool operator==(const TMapKey& o) const { return ptr == o.ptr && rows == o.rows && box_rows == o.box_rows; }
+};
+struct TMapHash {
+    size_t operator()(const TMapKey& k) const {
+        return reinterpret_cast<size_t>(k.ptr) ^ ((size_t)k.rows * 0x9E3779B97F4A7C15ull) ^ ((size_t)k.box_rows << 50);
+    }
+};
+// One layer of the cache, [page][K|V][kv head][slot][HD], seen as a matrix of HD-wide rows, in
+// boxes of 64 columns x box_rows rows with the 128-byte swizzle.
+int decode_cache_map(const void* ptr, long long rows, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<TMapKey, CUtensorMap, TMapHash> cache;
+    static EncodeTiledFn fn = nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    const TMapKey key{ptr, rows, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return (int)cudaErrorNotSupported;
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return (int)cudaErrorInvalidValue;
+    if (cache.size() > 1024) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+bool decode_tma_takes(int page_size) {
+    static const bool off = getenv("RUSTINFER_B200_DECODE_ATTENTION") && !strcmp(getenv("RUSTINFER_B200_DECODE_ATTENTION"), "cp.async");
+    return !off && DWARPS == 4 &&
+           (page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0));
+}
+#endif
+
 int configure() {
     static int status = -1;
     if (status < 0) {
@@ -503,6 +846,10 @@ int configure() {
                                              (int)PREFILL_SMEM);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_SMEM);
+#if RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DECODE_TMA_SMEM);
+#endif
         status = (int)e;
     }
     return status;
@@ -516,6 +863,17 @@ RI_API int ri_attention_decode_ctas_per_sm() {
     const int by_smem = (int)((227 * 1024) / (DECODE_SMEM + 1024));
     const int by_threads = 2048 / DTHREADS;
     return by_smem < by_threads ? (by_smem < 1 ? 1 : by_smem) : by_threads;
+}
+// ... of the kernel that fetches keys and values by TMA (0: not built for this head size)
+RI_API int ri_attention_decode_tma_ctas_per_sm(int page_size) {
+#if RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128
+    if (!decode_tma_takes(page_size)) return 0;
+    const int by_smem = (int)((227 * 1024) / (DECODE_TMA_SMEM + 1024));
+    const int by_threads = 2048 / TTHREADS;
+    return by_smem < by_threads ? (by_smem < 1 ? 1 : by_smem) : by_threads;
+#else
+    return 0;
+#endif
 }
 
 // Tokens per prefill tile for a model with `group` q heads per kv head: 64 rows hold
@@ -548,7 +906,8 @@ RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int 
                                     const void* cache, const int* block_table, int table_stride,
                                     const int* cu_q, const int* kv_len, const int* entry_list,
                                     int n_entries, int Hq, int Hkv, int page_size, float scale, int window,
-                                    int splits, float* part_o, float* part_lse, void* stream) {
+                                    int splits, float* part_o, float* part_lse, long long n_pages, int* error,
+                                    void* stream) {
     if (n_entries <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0 || splits < 1 || (splits > 1 && (!part_o || !part_lse)))
         return (int)cudaErrorInvalidValue;
@@ -557,6 +916,23 @@ RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int 
     const int G = Hq / Hkv, Gc = G < 16 ? G : 16, chunks = (G + Gc - 1) / Gc;
     dim3 grid(Hkv * chunks, splits, n_entries);
     cudaStream_t s = (cudaStream_t)stream;
+#if RI_HEAD_DIM == 64 || RI_HEAD_DIM == 128
+    // with the cache's size and an error flag at hand, keys and values come by TMA
+    if (n_pages > 0 && error && decode_tma_takes(page_size) && (reinterpret_cast<uintptr_t>(cache) & 15) == 0) {
+        const int box_rows = page_size < DKT ? page_size : DKT;
+        CUtensorMap map;
+        st = decode_cache_map(cache, n_pages * 2 * Hkv * page_size, box_rows, &map);
+        if (st != 0) return st;
+        RI_CHECKED(ri_launch(decode_tma_kernel, dim3(grid), dim3(TTHREADS), DECODE_TMA_SMEM, s, map,
+            (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, cu_q, kv_len, entry_list,
+            Hq, Hkv, Gc, chunks, page_size, box_rows, scale * 1.4426950408889634f, window, splits, part_o, part_lse, error));
+        st = ri_launch_status();
+        if (st != 0 || splits == 1) return st;
+        RI_CHECKED(ri_launch(combine_kernel, dim3(dim3(n_entries, Hq)), dim3(HD < 128 ? 64 : 128), 0, s,
+            part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits));
+        return ri_launch_status();
+    }
+#endif
     RI_CHECKED(ri_launch(decode_kernel, dim3(grid), dim3(DTHREADS), DECODE_SMEM, s, 
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_stride,
         cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,

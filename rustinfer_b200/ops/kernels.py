@@ -421,10 +421,11 @@ def decode_scratch_floats(entries: int, num_heads: int, head_dim: int, splits: i
 def attention_decode_bf16(q, out, cache, block_table, cu_q, kv_len, entry_list: Optional[torch.Tensor],
                           n_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                           window: Optional[int], splits: int, part_o: Optional[torch.Tensor],
-                          part_lse: Optional[torch.Tensor]) -> None:
+                          part_lse: Optional[torch.Tensor], by_tma: bool = True) -> None:
     """Entries of one token each (entry_list: their indices, None = 0..n-1); `splits` > 1
     cuts each entry's keys into that many ranges whose partial results go through
-    part_o / part_lse (fp32 scratch)."""
+    part_o / part_lse (fp32 scratch).  Head sizes 64 and 128 with pages of 8, 16, 32 or a
+    multiple of 64 keys fetch keys and values by TMA unless `by_tma` is False."""
     _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim)
     require_cuda(entry_list, part_o, part_lse)
     _i32(entry_list, "entry_list")
@@ -438,6 +439,7 @@ def attention_decode_bf16(q, out, cache, block_table, cu_q, kv_len, entry_list: 
                                        block_table.stride(0), _p(cu_q), _p(kv_len), _p(entry_list), n_entries,
                                        num_heads, num_kv_heads, cache.shape[3], float(scale),
                                        int(window) if window else 0, int(splits), _p(part_o), _p(part_lse),
+                                       cache.shape[0] if by_tma else 0, _p(gemm_tc_state(q.device)[2]),
                                        stream_ptr()), "attention_decode_bf16", 2 if splits > 1 else 1)
 
 

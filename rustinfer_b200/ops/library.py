@@ -29,7 +29,7 @@ _SIGNATURES = {
     "ri_decode_feedback": [_P, _P, _I, _P, _P, _I, _P, _P, _P],
     "ri_sample": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-    "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _P],
+    "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _L, _P, _P],
     "ri_attention_mma_tokens_per_tile": [_I],
     "ri_attention_prefill_tc": [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "ri_attention_tc_supports": [_I, _I, _I],
@@ -119,6 +119,8 @@ def attention_mma(head_dim: int) -> ctypes.CDLL:
         defines += [f"RI_DEC_WARPS={int(w)}", f"RI_DEC_STAGES={int(st)}"]
     lib = _load(name, ["attention_mma.cu"], defines)
     lib.ri_attention_decode_ctas_per_sm.restype = _I
+    lib.ri_attention_decode_tma_ctas_per_sm.restype = _I
+    lib.ri_attention_decode_tma_ctas_per_sm.argtypes = [_I]
     lib.ri_attention_decode_tile_keys.restype = _I
     return lib
 

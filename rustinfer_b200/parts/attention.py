@@ -79,7 +79,9 @@ class GQAAttention(Mixer):
                                    torch.empty(nl, dtype=torch.float32, device=ctx.device))
             self.part_o, self.part_lse = ctx.shared[key]
             lib = L.attention_mma(self.hd)
-            self.decode_ctas_per_sm = int(lib.ri_attention_decode_ctas_per_sm())
+            # the kernel that fetches keys and values by TMA where it is built for this geometry
+            self.decode_ctas_per_sm = (int(lib.ri_attention_decode_tma_ctas_per_sm(ctx.page_size))
+                                       or int(lib.ri_attention_decode_ctas_per_sm()))
             self.decode_tile_keys = int(lib.ri_attention_decode_tile_keys())
         else:
             self.attention_tile_rows = (16,)
