@@ -503,12 +503,15 @@ bool plan_layout(const RiChainPhase* phases, int n_phases, int M, int sms, Layou
             L->nw_bytes = max(L->nw_bytes, round_up(phases[i].K * (phases[i].norm_w_dtype == RI_BF16 ? 2 : 4), 1024));
         }
     }
+    // rows of the stream staged at a time: as many as leave the ring three stages, at least one
+    const int fixed = SMEM_LIMIT - 1024 - HEAD_BYTES - L->xs_bytes - L->nw_bytes;
     if (k_norm > 0) {
         if (k_norm * 4 > ROW_STAGE_BYTES) return false;
         L->stage_rows = min(M, ROW_STAGE_BYTES / (k_norm * 4));
+        while (L->stage_rows > 1 && fixed - round_up(L->stage_rows * k_norm * 4, 1024) < 3 * STAGE_BYTES) --L->stage_rows;
         L->stage_bytes = round_up(L->stage_rows * k_norm * 4, 1024);
     }
-    const int ring = SMEM_LIMIT - 1024 - HEAD_BYTES - L->xs_bytes - L->stage_bytes - L->nw_bytes;
+    const int ring = fixed - L->stage_bytes;
     L->stages = min(MAX_STAGES, ring / STAGE_BYTES);
     return L->stages >= 2;
 }

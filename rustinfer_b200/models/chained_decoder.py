@@ -99,7 +99,7 @@ class ChainedDecoder:
                 return None
         self = cls(decoder, 0)
         tokens = 0
-        for t in (16, K.CHAIN_MAX_TOKENS):                 # the widest step every chain of the model takes
+        for t in (8, 16, K.CHAIN_MAX_TOKENS):              # the widest step every chain of the model takes
             if all(K.decode_chain_fits(products, t, ctx.num_sms) for products, _ in self._chains(t, None, None)):
                 tokens = t
         limit = int(os.environ.get("RUSTINFER_B200_DECODE_CHAIN_TOKENS", "16"))

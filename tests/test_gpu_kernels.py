@@ -235,6 +235,8 @@ def test_rope_scatter(dt, Hq, Hkv, hd, rot, page):
 
 @pytest.mark.parametrize("M,hidden,inter,Hq,Hkv,hd,rot,page", [
     (8, 2048, 8192, 32, 8, 64, 64, 16),          # the shapes of a 1B decoder
+    (4, 4096, 14336, 32, 8, 128, 128, 16),        # ... of an 8B one: rows of the stream staged four at a time
+    (12, 3072, 8192, 24, 8, 128, 128, 32),        # ... of a 3B one, more than 8 tokens
     (5, 272, 552, 6, 2, 48, 32, 8),               # nothing a power of two, part of each head rotates
     (19, 520, 1040, 5, 5, 32, 32, 4),             # more than 16 tokens: the wider tile
     (1, 136, 96, 3, 1, 16, 16, 16),
