@@ -231,7 +231,12 @@ class ModelRunner:
         if num_pages is None:
             num_pages = self._auto_pages(mem_fraction_static)
         self.num_pages = int(num_pages)
-        self.capture_sizes = sorted(set(int(c) for c in (capture_sizes or ())))
+        # graph buckets: the sizes asked for that fit, and the largest batch itself when a larger
+        # size was asked for (else steps between the last fitting size and the limit would run eagerly)
+        sizes = set(int(c) for c in (capture_sizes or ()))
+        if any(c > self.max_batch_seqs for c in sizes):
+            sizes.add(self.max_batch_seqs)
+        self.capture_sizes = sorted(c for c in sizes if 1 <= c <= self.max_batch_seqs)
         self.cache = CacheManager(self.layout, [self.num_pages] * len(paged), self.page_size,
                                   self.max_batch_seqs)
         self._alloc_storage()
