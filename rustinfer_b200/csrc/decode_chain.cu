@@ -27,29 +27,7 @@
 #include "tc_primitives.cuh"
 #include <cuda.h>
 
-// One product of a chain, as the caller describes it.
-struct RiChainPhase {
-    const void* w;              // bf16 [N][K], K a multiple of 8, 16-byte aligned
-    int N, K;
-    int x_kind;                 // 0: x is bf16 [M][ld_x]; 1: x is the fp32 stream [M][ld_x] and the
-    int ld_x;                   //    operand is x * norm_w * rsqrt(mean(x^2) + eps)
-    int x_rows;                 // rows the matrix x really has (a TMA box reads 8, 16 or 32 of them)
-    const void* x;
-    const void* norm_w;
-    int norm_w_dtype;
-    float eps;
-    int out_kind;               // 0: fp32 out += product; 1: bf16 out[M][N/2] = silu(gate) * up over
-    int ld_out;                 //    alternating weight rows; 2: bf16 out = product
-    void* out;
-};
-
-struct RiChainRope {
-    float* qkv; int ld;
-    const int* positions; const float* cos_t; const float* sin_t; const int* slot_of_token;
-    void* q_out; int ld_q;
-    void* cache;
-    int Hq, Hkv, hd, rot, page_size;
-};
+#include "decode_chain_api.h"
 
 namespace {
 using namespace ri_tc;
@@ -289,7 +267,10 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                     unsigned char* nws = base + p.nw_off;
                     const int upr = P.K >> 3;                               // units of 8 floats in a row
                     const int k_lo = kb0 * BK, k_hi = (kb0 + n_kb) * BK;
-                    const unsigned nw_bytes = (unsigned)P.K * (P.norm_w_bf16 ? 2u : 4u);
+                    const int Kc = P.K, x_kb_bytes = p.x_kb_bytes;
+                    const bool nw_bf16 = P.norm_w_bf16 != 0;
+                    const float eps = P.eps;
+                    const unsigned nw_bytes = (unsigned)Kc * (nw_bf16 ? 2u : 4u);
                     for (int r0 = 0; r0 < M && ok; r0 += p.stage_rows) {
                         const int rows = min(p.stage_rows, M - r0);
                         if (threadIdx.x == 64) {
@@ -302,7 +283,7 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                         ok = mbar_wait(x_land, xl & 1, p.error, ERR_CHAIN_EPILOGUE);
                         ++xl;
                         for (int r = quarter; r < rows && ok; r += 4) {
-                            const float* row = stg + (size_t)r * P.K;
+                            const float* row = stg + (size_t)r * Kc;
                             const int rr = r0 + r;
                             float ss = 0.f;
                             for (int u = lane; u < upr; u += 32) {
@@ -313,7 +294,7 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                                     + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
                                 if (k >= k_lo && k < k_hi) {
                                     float w[8];
-                                    if (P.norm_w_bf16) {
+                                    if (nw_bf16) {
                                         const uint4 wv = *reinterpret_cast<const uint4*>(nws + (size_t)k * 2);
                                         const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
@@ -329,11 +310,11 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                                     float x[8];
                                     x[0] = x0.x * w[0]; x[1] = x0.y * w[1]; x[2] = x0.z * w[2]; x[3] = x0.w * w[3];
                                     x[4] = x1.x * w[4]; x[5] = x1.y * w[5]; x[6] = x1.z * w[6]; x[7] = x1.w * w[7];
-                                    *reinterpret_cast<uint4*>(xs + (size_t)((k >> 6) - kb0) * p.x_kb_bytes + rr * 128 + (((u & 7) ^ (rr & 7)) << 4)) = pack8(x);
+                                    *reinterpret_cast<uint4*>(xs + (size_t)((k >> 6) - kb0) * x_kb_bytes + rr * 128 + (((u & 7) ^ (rr & 7)) << 4)) = pack8(x);
                                 }
                             }
                             ss = warp_sum(ss);
-                            if (lane == 0) row_scale[rr] = 1.0f / sqrtf(ss / (float)P.K + P.eps);
+                            if (lane == 0) row_scale[rr] = 1.0f / sqrtf(ss / (float)Kc + eps);
                         }
                         // the staged rows may be overwritten, the scales are there for all warps
                         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -352,21 +333,46 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                 tc_fence_after();
                 const int fl = quarter * 32 + lane;
                 const int feat = fl < P.a_box ? tile * P.a_box + fl : 0x3fffffff;
-                for (int c0 = 0; c0 < M && ok; c0 += 4) {
-                    float v[4];
-                    tmem_ld4(taddr + c0, v);
+                // The product's numbers go into registers first: read through `P` inside the loops
+                // they are fetched from the parameter bank again after every asm statement, which
+                // made a token cost 270 cycles.
+                const int out_kind = P.out_kind, ld_out = P.ld_out;
+                const bool scaled = P.x_kind == X_NORM, live = feat < P.N;
+                if (out_kind == OUT_ADD_F32) {
+                    float* o = reinterpret_cast<float*>(P.out) + (live ? feat : 0);
+                    for (int c0 = 0; c0 < M && ok; c0 += 4) {
+                        float v[4];
+                        tmem_ld4(taddr + c0, v);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int tok = c0 + j;
-                        const float a = P.x_kind == X_NORM ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
-                        const float up = __shfl_xor_sync(0xffffffffu, a, 1);       // SiLU: even lane gate, odd lane up
-                        if (tok < M && feat < P.N) {
-                            if (P.out_kind == OUT_ADD_F32)
-                                atomicAdd(reinterpret_cast<float*>(P.out) + (size_t)tok * P.ld_out + feat, a);
-                            else if (P.out_kind == OUT_BF16)
-                                reinterpret_cast<bf16*>(P.out)[(size_t)tok * P.ld_out + feat] = __float2bfloat16_rn(a);
-                            else if ((lane & 1) == 0)
-                                reinterpret_cast<bf16*>(P.out)[(size_t)tok * P.ld_out + (feat >> 1)] = __float2bfloat16_rn(silu_mul(a, up));
+                        for (int j = 0; j < 4; ++j) {
+                            const int tok = c0 + j;
+                            const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
+                            if (tok < M && live) atomicAdd(o + (size_t)tok * ld_out, a);
+                        }
+                    }
+                } else if (out_kind == OUT_BF16) {
+                    bf16* o = reinterpret_cast<bf16*>(P.out) + (live ? feat : 0);
+                    for (int c0 = 0; c0 < M && ok; c0 += 4) {
+                        float v[4];
+                        tmem_ld4(taddr + c0, v);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int tok = c0 + j;
+                            const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
+                            if (tok < M && live) o[(size_t)tok * ld_out] = __float2bfloat16_rn(a);
+                        }
+                    }
+                } else {
+                    bf16* o = reinterpret_cast<bf16*>(P.out) + (live ? (feat >> 1) : 0);
+                    for (int c0 = 0; c0 < M && ok; c0 += 4) {
+                        float v[4];
+                        tmem_ld4(taddr + c0, v);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int tok = c0 + j;
+                            const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
+                            const float up = __shfl_xor_sync(0xffffffffu, a, 1);   // even lane gate, odd lane up
+                            if (tok < M && live && (lane & 1) == 0) o[(size_t)tok * ld_out] = __float2bfloat16_rn(silu_mul(a, up));
                         }
                     }
                 }
@@ -489,7 +495,7 @@ bool plan_phase(const RiChainPhase& f, int sms, int* a_box, int* tiles, int* spl
 }
 
 bool plan_layout(const RiChainPhase* phases, int n_phases, int M, int sms, Layout* L) {
-    if (n_phases < 1 || n_phases > MAX_PHASES || M < 1 || M > 32 || sms < 1) return false;
+    if (n_phases < 1 || n_phases > MAX_PHASES || M < 1 || M > 16 || sms < 1) return false;
     L->bn = M <= 16 ? 16 : 32;
     L->x_kb_bytes = M <= 8 ? 1024 : L->bn * BK * 2;           // 8 tokens: one group of 8 rows, read twice
     L->xs_bytes = 0; L->stage_bytes = 0; L->nw_bytes = 0; L->stage_rows = 1;
@@ -520,12 +526,14 @@ bool plan_layout(const RiChainPhase* phases, int n_phases, int M, int sms, Layou
 // Whether the chain can run these products with `M` tokens (1) or not (0): the caller uses
 // this to decide between the chain and separate kernels.
 RI_API int ri_decode_chain_fits(const RiChainPhase* phases, int n_phases, int M, int sms) {
+    if (M > 16) return ri_decode_chain_wide_fits(phases, n_phases, M, sms);
     Layout L;
     return phases && plan_layout(phases, n_phases, M, sms, &L) ? 1 : 0;
 }
 
 RI_API int ri_decode_chain(const RiChainPhase* phases, int n_phases, const RiChainRope* rope, int M,
                            unsigned* grid_bar, int* error, int sms, void* stream) {
+    if (M > 16) return ri_decode_chain_wide(phases, n_phases, rope, M, grid_bar, error, sms, stream);
     Layout L;
     if (!phases || !grid_bar || !error || !plan_layout(phases, n_phases, M, sms, &L)) return (int)cudaErrorInvalidValue;
     Maps maps;

@@ -51,6 +51,9 @@ class ChainedDecoder:
             need[("q", a.Hq * a.hd, torch.bfloat16)] = None
             need[("attn", a.Hq * a.hd, torch.bfloat16)] = None
             need[("mid", f.inter, torch.bfloat16)] = None
+            need[("xn", a.hidden, torch.bfloat16)] = None            # wide steps: the normed operand
+        need[("rowsq_a", 1, torch.float32)] = None                   # ... and the rows' sums of squares
+        need[("rowsq_b", 1, torch.float32)] = None
         norms = [n for block in decoder.blocks for n in (block.mixer_norm, block.ffn_norm)]
         size = sum(-(-n.weight.numel() * n.weight.element_size() // 256) * 256 for n in norms)
         size += sum(-(-rows * cols * torch.empty((), dtype=dt).element_size() // 256) * 256 for _, cols, dt in need)
@@ -99,10 +102,10 @@ class ChainedDecoder:
                 return None
         self = cls(decoder, 0)
         tokens = 0
-        for t in (8, 16, K.CHAIN_MAX_TOKENS):              # the widest step every chain of the model takes
+        for t in (8, 16, 32, K.CHAIN_MAX_TOKENS):          # the widest step every chain of the model takes
             if all(K.decode_chain_fits(products, t, ctx.num_sms) for products, _ in self._chains(t, None, None)):
                 tokens = t
-        limit = int(os.environ.get("RUSTINFER_B200_DECODE_CHAIN_TOKENS", "16"))
+        limit = int(os.environ.get("RUSTINFER_B200_DECODE_CHAIN_TOKENS", str(K.CHAIN_MAX_TOKENS)))
         self.max_tokens = min(tokens, limit)
         return self if self.max_tokens > 0 else None
 
@@ -112,7 +115,9 @@ class ChainedDecoder:
         width = a.qkv.out_features
         acc = self._buffer("qkv", width, torch.float32)
         return K.ChainProduct(a.qkv.weight, self.h[:T], acc[:T], K.CHAIN_ADD_F32,
-                              norm=(self.norm_w[id(block.mixer_norm)], block.mixer_norm.eps))
+                              norm=(self.norm_w[id(block.mixer_norm)], block.mixer_norm.eps),
+                              xn=self._buffer("xn", a.hidden, torch.bfloat16),
+                              rowsq=self._buffer("rowsq_b", 1, torch.float32).view(-1))
 
     def _rope(self, block, T, step: Optional[StepContext], cache: Optional[PagedLayerCache]):
         a = block.mixer
@@ -138,7 +143,9 @@ class ChainedDecoder:
             rows = K.CHAIN_MAX_TOKENS
             products = [K.ChainProduct(a.o.weight, attn[:T], self.h[:T], K.CHAIN_ADD_F32, x_rows=rows),
                         K.ChainProduct(f.gate_up.weight, self.h[:T], mid[:T], K.CHAIN_SILU_BF16,
-                                       norm=(self.norm_w[id(block.ffn_norm)], block.ffn_norm.eps)),
+                                       norm=(self.norm_w[id(block.ffn_norm)], block.ffn_norm.eps),
+                                       xn=self._buffer("xn", a.hidden, torch.bfloat16),
+                                       rowsq=self._buffer("rowsq_a", 1, torch.float32).view(-1)),
                         K.ChainProduct(f.down.weight, mid[:T], self.h[:T], K.CHAIN_ADD_F32, x_rows=rows)]
             rope = None
             if i + 1 < len(self.entries):

@@ -212,7 +212,8 @@ class _ChainPhase(ctypes.Structure):
     _fields_ = [("w", ctypes.c_void_p), ("N", ctypes.c_int), ("K", ctypes.c_int), ("x_kind", ctypes.c_int),
                 ("ld_x", ctypes.c_int), ("x_rows", ctypes.c_int), ("x", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
                 ("norm_w_dtype", ctypes.c_int), ("eps", ctypes.c_float), ("out_kind", ctypes.c_int),
-                ("ld_out", ctypes.c_int), ("out", ctypes.c_void_p)]
+                ("ld_out", ctypes.c_int), ("out", ctypes.c_void_p), ("xn", ctypes.c_void_p),
+                ("rowsq", ctypes.c_void_p)]
 
 
 class _ChainRope(ctypes.Structure):
@@ -224,7 +225,7 @@ class _ChainRope(ctypes.Structure):
 
 
 CHAIN_ADD_F32, CHAIN_SILU_BF16, CHAIN_BF16 = 0, 1, 2
-CHAIN_MAX_TOKENS, CHAIN_MAX_PRODUCTS = 32, 6
+CHAIN_MAX_TOKENS, CHAIN_MAX_PRODUCTS = 64, 6
 
 
 class ChainProduct:
@@ -235,8 +236,16 @@ class ChainProduct:
     CHAIN_BF16 stores bf16 [M, N]."""
 
     def __init__(self, w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, out_kind: int, norm=None,
-                 x_rows: Optional[int] = None):
+                 x_rows: Optional[int] = None, xn: Optional[torch.Tensor] = None,
+                 rowsq: Optional[torch.Tensor] = None):
         self.w, self.x, self.out, self.out_kind, self.norm = w, x, out, out_kind, norm
+        # steps of more than 16 tokens with a norm: room for the normed operand, bf16 [64, K], and
+        # for the rows' sums of squares, fp32 [64], zero before the first use (the kernel leaves it zero)
+        self.xn, self.rowsq = xn, rowsq
+        if norm is not None and xn is not None and (xn.dtype != torch.bfloat16 or tuple(xn.shape) != (CHAIN_MAX_TOKENS, w.shape[1])
+                                                  or not xn.is_contiguous() or rowsq is None or rowsq.dtype != torch.float32
+                                                  or rowsq.numel() != CHAIN_MAX_TOKENS):
+            raise KernelError("decode_chain: the room for the normed operand does not fit")
         # rows behind x that may be read (not used): a bf16 x is fetched in boxes of 8, 16 or 32 rows
         self.x_rows = x.shape[0] if x_rows is None else x_rows
         N, Kd = w.shape
@@ -258,6 +267,8 @@ class ChainProduct:
         else:
             c.norm_w, c.norm_w_dtype, c.eps = None, 0, 0.0
         c.out, c.ld_out, c.out_kind = self.out.data_ptr(), self.out.stride(0), self.out_kind
+        c.xn = self.xn.data_ptr() if self.xn is not None else None
+        c.rowsq = self.rowsq.data_ptr() if self.rowsq is not None else None
 
 
 class ChainRope:

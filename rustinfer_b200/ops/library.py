@@ -95,7 +95,7 @@ def attention_plain(head_dim: int) -> ctypes.CDLL:
 
 
 def gemm_tc() -> ctypes.CDLL:
-    lib = _load("ri_gemm_tc", ["gemm_tc.cu", "decode_chain.cu"])
+    lib = _load("ri_gemm_tc", ["gemm_tc.cu", "decode_chain.cu", "decode_chain_wide.cu"])
     kb = os.environ.get("RUSTINFER_B200_STREAM_KB")
     if kb and not getattr(lib, "_budget_set", False):
         lib.ri_gemm_tc_set_stream_budget.argtypes = [_I]

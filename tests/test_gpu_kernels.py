@@ -238,7 +238,9 @@ def test_rope_scatter(dt, Hq, Hkv, hd, rot, page):
     (4, 4096, 14336, 32, 8, 128, 128, 16),        # ... of an 8B one: rows of the stream staged four at a time
     (12, 3072, 8192, 24, 8, 128, 128, 32),        # ... of a 3B one, more than 8 tokens
     (5, 272, 552, 6, 2, 48, 32, 8),               # nothing a power of two, part of each head rotates
-    (19, 520, 1040, 5, 5, 32, 32, 4),             # more than 16 tokens: the wider tile
+    (19, 520, 1040, 5, 5, 32, 32, 4),             # more than 16 tokens: the operand streams with the weights
+    (40, 2048, 8192, 32, 8, 64, 64, 16),          # ... 33 or more: 64-token tiles
+    (64, 272, 552, 6, 2, 48, 32, 8),
     (1, 136, 96, 3, 1, 16, 16, 16),
 ])
 def test_decode_chain(M, hidden, inter, Hq, Hkv, hd, rot, page):
@@ -258,12 +260,14 @@ def test_decode_chain(M, hidden, inter, Hq, Hkv, hd, rot, page):
     n1_d, n2_d = bf(n1), n2.to(d)                                                        # one norm weight in each dtype
     attn = torch.randn(M, qdim)
     h0 = torch.randn(M, hidden) * 2
-    rows = 32                                                                            # buffers hold more rows than are used
+    rows = 64                                                                            # buffers hold more rows than are used
     attn_d = torch.zeros(rows, qdim, dtype=torch.bfloat16, device=d); attn_d[:M] = bf(attn)
     h_d = torch.zeros(rows, hidden, dtype=torch.float32, device=d); h_d[:M] = h0.to(d)
     m_d = torch.full((rows, inter), 9.0, dtype=torch.bfloat16, device=d)
     qkv_d = torch.zeros(rows, width, dtype=torch.float32, device=d)
     q_d = torch.full((rows, qdim), 9.0, dtype=torch.bfloat16, device=d)
+    xn_d = torch.zeros(rows, hidden, dtype=torch.bfloat16, device=d)                      # wide steps only
+    sq_a, sq_b = torch.zeros(rows, device=d), torch.zeros(rows, device=d)
     pages, maxpos = 12, 300
     pos = torch.randint(0, maxpos, (rows,), dtype=torch.int32)
     c, s_ = _rope_tables(maxpos, rot)
@@ -272,9 +276,9 @@ def test_decode_chain(M, hidden, inter, Hq, Hkv, hd, rot, page):
         slots[2] = -1                                                                    # a token that is not stored
     cache = torch.full((pages, 2, Hkv, page, hd), 7.0, dtype=torch.bfloat16, device=d)
     products = [k.ChainProduct(wo_d, attn_d, h_d, k.CHAIN_ADD_F32),
-                k.ChainProduct(wgu_d, h_d, m_d, k.CHAIN_SILU_BF16, norm=(n1_d, 1e-5)),
+                k.ChainProduct(wgu_d, h_d, m_d, k.CHAIN_SILU_BF16, norm=(n1_d, 1e-5), xn=xn_d, rowsq=sq_a),
                 k.ChainProduct(wd_d, m_d, h_d, k.CHAIN_ADD_F32),
-                k.ChainProduct(wqkv_d, h_d, qkv_d, k.CHAIN_ADD_F32, norm=(n2_d, 3e-6))]
+                k.ChainProduct(wqkv_d, h_d, qkv_d, k.CHAIN_ADD_F32, norm=(n2_d, 3e-6), xn=xn_d, rowsq=sq_b)]
     rope = k.ChainRope(qkv_d, pos.to(d), c.float().to(d), s_.float().to(d), slots.to(d), q_d, cache, Hq, Hkv, hd, rot)
     assert k.decode_chain_fits(products, M, 148)
     for _ in range(2):                                       # twice: the barrier and the q,k,v buffer reset themselves
@@ -309,6 +313,7 @@ def test_decode_chain(M, hidden, inter, Hq, Hkv, hd, rot, page):
     untouched = want == 7.0
     assert torch.equal(cache.double().cpu()[untouched], want[untouched])
     assert torch.count_nonzero(qkv_d) == 0                   # left at zero for the next chain
+    assert torch.count_nonzero(sq_a) == 0 and torch.count_nonzero(sq_b) == 0
 
 
 class PagedCase:

@@ -12,6 +12,13 @@ from helpers import rel_err
 
 pytestmark = pytest.mark.gpu
 
+# max |engine - plain| / max |plain| over logits.  fp32: sums of a few hundred fp32 products
+# against float64.  bf16: the same bound as the replay tests use (see the measured spread there);
+# on these toy models with weights of 0.2 one cut lands at 3.5e-2 and another at 4.0e-2 depending
+# only on which kernels round q and k (the chain rounds them once, from fp32).
+LOGITS_TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+
+
 DT = [torch.float32, torch.bfloat16]
 TOLP = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
 
@@ -252,7 +259,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path, dtype):
     _, w = P.read_model_folder(folder)
     g = torch.Generator().manual_seed(0)
     a, b = (torch.randint(0, 97, (n,), generator=g).tolist() for n in (40, 23))
-    tol = 2e-5 if dtype == "float32" else 4e-2
+    tol = LOGITS_TOL[dtype]
     # two requests, cut differently and mixed in the same steps; state must carry across cuts
     r.open("a"), r.open("b")
     got_a, got_b = [], []
@@ -348,7 +355,7 @@ def test_run_order_shared_cache_and_window_group(tmp_path, dtype):
     g = torch.Generator().manual_seed(1)
     ids = torch.randint(0, 113, (60,), generator=g).tolist()
     ref = _arranged_plain(cfg, w, ids)
-    tol = 2e-5 if dtype == "float32" else 4e-2
+    tol = LOGITS_TOL[dtype]
     for cuts in ([60], [7, 20, 1, 1, 1, 2, 28], [1] * 60):
         r.open("a")
         outs, at = [], 0
