@@ -160,19 +160,22 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
         int it = 0;
         for (int ph = 0; ph < p.n_phases && ok; ++ph) {
             const Phase& P = p.ph[ph];
+            // (copied out: a field read through P inside the loop is fetched from the parameter bank each time)
+            const int a_box = P.a_box, tiles = P.tiles, items = P.tiles * P.splits, per = P.per;
             const int kblocks = (P.K + KSTEP - 1) / KSTEP;
-            const unsigned tx = (unsigned)P.a_box * BK * 2 * SUBS;     // a box past the last column still counts, as zeros
-            for (int item = blockIdx.x; item < P.tiles * P.splits && ok; item += G) {
-                const int tile = item % P.tiles, kb0 = (item / P.tiles) * P.per;
-                const int n_kb = min(P.per, kblocks - kb0);
+            const unsigned tx = (unsigned)a_box * BK * 2 * SUBS;       // a box past the last column still counts, as zeros
+            const CUtensorMap* wmap = &maps.m[ph];
+            for (int item = blockIdx.x; item < items && ok; item += G) {
+                const int tile = item % tiles, kb0 = (item / tiles) * per;
+                const int n_kb = min(per, kblocks - kb0);
                 for (int i = 0; i < n_kb; ++i, ++it) {
                     const int s = it % STAGES, round = it / STAGES;
                     if (round > 0 && !mbar_wait(&empty[s], (round - 1) & 1, p.error, ERR_CHAIN_PRODUCER)) { ok = false; break; }
                     mbar_expect_tx(&full[s], tx);
 #pragma unroll
                     for (int h = 0; h < SUBS; ++h)
-                        tma_load_2d(ring + (size_t)s * STAGE_BYTES + h * SUB_BYTES, &maps.m[ph], &full[s],
-                                    (kb0 + i) * KSTEP + h * BK, tile * P.a_box);
+                        tma_load_2d(ring + (size_t)s * STAGE_BYTES + h * SUB_BYTES, wmap, &full[s],
+                                    (kb0 + i) * KSTEP + h * BK, tile * a_box);
                 }
             }
         }
