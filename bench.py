@@ -1,6 +1,6 @@
 """Decode and prefill throughput of the engine on one B200, in the contract's one JSON line.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--shape 1b|3b|8b]
 
 A step is one decode step of the whole batch.  The default run has the layer sizes of the
 Llama-3.2-1B-shaped benchmark configuration with random weights ~N(0, 0.02) (seed 2), a
@@ -9,6 +9,8 @@ timed on the device over K steps fed with the previous step's tokens on the devi
 is the same through `Engine.add_request` / `Engine.step`, host token ids in and out.
 Also reported: a 2,048-token prefill, the decode step against the HBM roofline, decode at
 batch 1 and 64, clocks sampled while timing, and how many of this package's kernels ran.
+`--shape` takes the layer sizes of the 3B or 8B benchmark configuration instead; `--only
+decode|prefill|serve` runs one part alone and prints its time.
 """
 from __future__ import annotations
 
@@ -25,13 +27,20 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Llama-3.2-1B-shaped
-MODEL = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=16,
-             hidden_size=2048, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
-             intermediate_size=8192, vocab_size=128256, rope_theta=500000.0,
-             rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
-                               original_max_position_embeddings=8192),
-             rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
+def _llama(layers, hidden, heads, kv_heads, head_dim, inter, factor, tied):
+    return dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=layers,
+                hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
+                intermediate_size=inter, vocab_size=128256, rope_theta=500000.0,
+                rope_scaling=dict(rope_type="llama3", factor=factor, low_freq_factor=1.0, high_freq_factor=4.0,
+                                  original_max_position_embeddings=8192),
+                rms_norm_eps=1e-5, tie_word_embeddings=tied, max_position_embeddings=131072)
+
+
+# the benchmark configurations: the Llama-3.2-1B shape is the default and the headline; the
+# 3B and 8B shapes are there for --shape (further sizes, head size 128, an untied head)
+SHAPES = {"1b": ("Llama-3.2-1B-shaped", _llama(16, 2048, 32, 8, 64, 8192, 32.0, True)),
+          "3b": ("Llama-3.2-3B-shaped", _llama(28, 3072, 24, 8, 128, 8192, 32.0, True)),
+          "8b": ("Llama-3.1-8B-shaped", _llama(32, 4096, 32, 8, 128, 14336, 8.0, False))}
 SEED, STD = 2, 0.02
 CONTEXT, PREFILL_TOKENS, PAGE = 4096, 2048, 16
 NOMINAL_HBM_GBS, NOMINAL_BF16_TFLOPS = 6650.0, 1590.0      # fallback when no measured peaks are given
@@ -226,6 +235,33 @@ def prefill_timed(engine, vocab, tokens, repeats=3):
     return best, windows[1:]
 
 
+def serve_workload(folder, vocab, layers):
+    """Continuous batching through the public entry point: 64 requests arrive at once, prompt
+    lengths uniform in [128, 2048], 256 tokens out each, prompts computed in portions of 512
+    beside the decoding of the others.  Prints tokens a second over the whole run (host time:
+    scheduling, launches and the reading of every token included)."""
+    import random
+    import torch
+    from rustinfer_b200.engine.engine import Engine
+    from rustinfer_b200.sampling.params import SamplingParams
+    engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=64, max_model_len=CONTEXT,
+                    paged_block_size=PAGE, chunked_prefill_size=512, num_blocks=64 * 2560 // PAGE,
+                    ignore_eos=True)
+    rng = random.Random(3)
+    prompts = [[rng.randrange(vocab) for _ in range(rng.randint(128, 2048))] for _ in range(64)]
+    engine.generate([p[:64] for p in prompts[:8]], SamplingParams(max_tokens=8, ignore_eos=True))   # warm-up
+    torch.cuda.synchronize()
+    steps0 = engine.stats.steps
+    t0 = time.perf_counter()
+    results = engine.generate(prompts, SamplingParams(max_tokens=256, ignore_eos=True))
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    n_in, n_out = sum(len(p) for p in prompts), sum(len(r.tokens) for r in results)
+    print(f"serve layers{layers}: {len(prompts)} requests, {n_in} prompt tokens, {n_out} tokens out in {dt:.3f} s: "
+          f"{n_out / dt:.0f} out tok/s, {(n_in + n_out) / dt:.0f} tok/s in all, {engine.stats.steps - steps0} steps, "
+          f"{engine.stats.preemptions} preemptions")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -233,11 +269,14 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+    ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the 1B shape)")
+    ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
-    ap.add_argument("--only", choices=["decode", "prefill"],
-                    help="run one part alone and print its time (for profiler captures; no JSON line)")
+    ap.add_argument("--only", choices=["decode", "prefill", "serve"],
+                    help="run one part alone and print its time (for profiler captures; no JSON line); "
+                         "serve: 64 requests, prompts of 128 to 2,048 tokens, 256 tokens out each, "
+                         "prompt portions of 512, through Engine.generate")
     ap.add_argument("--eager", action="store_true", help="with --only decode: no CUDA graphs")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
     args = ap.parse_args()
@@ -257,7 +296,10 @@ def main() -> int:
     from rustinfer_b200.weights.random_init import write_random_model
 
     hbm_gbs, bf16_tflops, peak_kind = peaks()
-    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    if args.layers <= 0:
+        args.layers = shape["num_hidden_layers"]
+    cfg = dict(shape, num_hidden_layers=args.layers)
     vocab = cfg["vocab_size"]
     per_layer, weight_bytes, kv_per_token, q_dim = model_numbers(cfg, args.layers)
     clocks = ClockSampler()
@@ -265,6 +307,10 @@ def main() -> int:
     windows = []
     with tempfile.TemporaryDirectory(prefix="rustinfer_b200_bench_") as tmp:
         folder = write_random_model(os.path.join(tmp, "model"), cfg, seed=SEED, std=STD)
+        if args.only == "serve":
+            serve_workload(folder, vocab, args.layers)
+            clocks.stop()
+            return 0
         if args.only:
             seqs = max(args.batch, 1)
             engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=seqs,
@@ -309,15 +355,15 @@ def main() -> int:
     prefill_flops = 2 * T * args.layers * per_layer + 2 * vocab * cfg["hidden_size"] + 2 * T * T * q_dim * args.layers
     prefill_frac = prefill_flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12)
     out = {
-        "metric": "decode tok/s @ batch 8, context 4096 (Llama-3.2-1B-shaped, bf16, random weights)",
+        "metric": f"decode tok/s @ batch {args.batch}, context {CONTEXT} ({shape_name}, bf16, random weights)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids",
-        "config": {"model": "Llama-3.2-1B-shaped", "global_batch": args.batch, "seq_len": CONTEXT,
-                   "parallelism": "single GPU", "layers": args.layers, "layers_full": MODEL["num_hidden_layers"],
+        "config": {"model": shape_name, "global_batch": args.batch, "seq_len": CONTEXT,
+                   "parallelism": "single GPU", "layers": args.layers, "layers_full": shape["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_head": True,
+                   "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_head": cfg["tie_word_embeddings"],
                    "page_size": PAGE, "prefill_tokens": T, "cuda_graphs": True,
                    "l2": "each step reads %.2f GB of weights and cache, far beyond the 126 MB L2" % (step_bytes / 1e9),
                    "peaks": peak_kind},

@@ -75,6 +75,7 @@ struct Params {
     int a_box;                           // rows of A per tile actually loaded (<= 128, a multiple of 8)
     int stages, stage_bytes;             // ring of operand stages: (a_box + BN) * 128 bytes each
     int budget;                          // bytes of the ring
+    int pair_bn;                         // width of a CTA pair's tile (256 or 192)
 };
 
 
@@ -462,11 +463,12 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, unsigned rank)
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const Params p) {
-    constexpr int BN = PAIR_BN, ACC_COLS = 256, TMEM_COLS = 512;
+    constexpr int ACC_COLS = 256, TMEM_COLS = 512;
+    const int BN = p.pair_bn, HALF_BN = BN >> 1;                  // 256, or 192 where that evens out the waves
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int STAGES = p.stages, STAGE_BYTES = p.stage_bytes;       // A 128 x 64 and half of B, 128 x 64: 32 KB
+    const int STAGES = p.stages, STAGE_BYTES = p.stage_bytes;       // A 128 x 64 and half of B, up to 128 x 64: 32 KB
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + p.budget + SMEM_TAIL);
     uint64_t* empty = full + MAX_STAGES;
     uint64_t* acc_full = empty + MAX_STAGES;
@@ -503,7 +505,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int it = 0, s = 0;
         unsigned par = 1;
         for (int tile = pair; tile < p.n_tiles && ok; tile += pairs) {
-            const int a0 = (tile % p.tiles_a) * 256 + (int)rank * BM, b0 = (tile / p.tiles_a) * BN + (int)rank * BM;
+            const int a0 = (tile % p.tiles_a) * 256 + (int)rank * BM, b0 = (tile / p.tiles_a) * BN + (int)rank * HALF_BN;
             for (int i = 0; i < n_kb; ++i, ++it) {
                 unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                 if (it >= STAGES && (s & 1) == 0 &&
@@ -516,7 +518,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
         // ------------------------------------------------------------ MMA issuer (even CTA only)
-        // D fp32, A and B bf16, both K-major, N = 256, M = 256 over the two CTAs
+        // D fp32, A and B bf16, both K-major, N = the tile's width, M = 256 over the two CTAs
         const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) | ((unsigned)(256 >> 4) << 24);
         const uint64_t desc0 = smem_desc(smem_u32(tiles));
         const unsigned stage_step = (unsigned)STAGE_BYTES >> 4, b_step = (unsigned)(BM * BK * 2) >> 4;
@@ -580,6 +582,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+int device_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t s) {
     static bool configured = false;
     if (!configured) {
@@ -587,12 +599,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, c
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    const int sms = device_sms();
     const int pairs = p.n_tiles < sms / 2 ? p.n_tiles : sms / 2;
     RI_CHECKED(ri_launch(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(THREADS), (size_t)p.budget + SMEM_EXTRA, s, ma, mb, p));
     return ri_launch_status();
@@ -613,12 +620,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, int ti
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    const int sms = device_sms();
     // one CTA per SM walks the tiles; with K slices every CTA has exactly one tile
     const int ctas = (p.splits > 1 || tiles < sms) ? tiles : sms;
     RI_CHECKED(ri_launch(gemm_tc_kernel<BN>, dim3(ctas, 1, p.splits), dim3(THREADS), (size_t)p.budget + SMEM_EXTRA, s, ma, mb, p));
@@ -660,6 +662,7 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     const void* A = swap ? W : X;
     const void* B = swap ? X : W;
     Params p;
+    p.pair_bn = 0;
     p.a_rows = swap ? N : M;
     p.b_rows = swap ? M : N;
     p.K = K; p.swap = swap; p.epilogue = epilogue; p.out = out; p.ld_out = ld_out; p.splits = splits;
@@ -687,14 +690,25 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     // many tokens: a 256 x 256 tile on a CTA pair (less operand traffic per flop)
     static const bool pair_off = getenv("RUSTINFER_B200_GEMM_PAIR") && atoi(getenv("RUSTINFER_B200_GEMM_PAIR")) == 0;
     if (!swap && bn == PAIR_BN && splits == 1 && a_box == BM && !pair_off && p.a_rows >= 512) {
-        p.stage_bytes = 2 * BM * BK * 2;
+        // the width of a tile: 256, or 192 where fewer columns in the last wave of tiles cost less
+        // than narrower tiles do (3072 features of 2048 tokens: 96 tiles of 256 are two waves on
+        // 74 pairs, 512 columns deep; 128 tiles of 192 are two waves too, 384 deep)
+        p.tiles_a = (p.a_rows + 255) / 256;
+        const int pairs = device_sms() / 2;
+        long long best = 0;
+        p.pair_bn = PAIR_BN;
+        for (int w : {256, 192}) {
+            const long long tiles = (long long)p.tiles_a * ((p.b_rows + w - 1) / w);
+            const long long depth = ((tiles + pairs - 1) / pairs) * w;
+            if (best == 0 || depth < best) { best = depth; p.pair_bn = w; }
+        }
+        p.stage_bytes = (BM + p.pair_bn / 2) * BK * 2;
         p.stages = (p.budget / p.stage_bytes) & ~1;
         if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
-        p.tiles_a = (p.a_rows + 255) / 256;
-        p.n_tiles = p.tiles_a * ((p.b_rows + PAIR_BN - 1) / PAIR_BN);
+        p.n_tiles = p.tiles_a * ((p.b_rows + p.pair_bn - 1) / p.pair_bn);
         int stp = make_map(A, p.a_rows, K, BM, &ma);
         if (stp != 0) return stp;
-        stp = make_map(B, p.b_rows, K, BM, &mb);
+        stp = make_map(B, p.b_rows, K, p.pair_bn / 2, &mb);
         if (stp != 0) return stp;
         return launch_pair(ma, mb, p, (cudaStream_t)stream);
     }

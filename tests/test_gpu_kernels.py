@@ -121,10 +121,12 @@ def test_gemm_f32_is_exact_fp32(M, N, K_):
     assert torch.allclose(out.double().cpu(), wide[:, 8: 8 + K_].double().cpu() @ w.double().cpu().T, atol=bound)
 
 
-# the last three have 512 tokens or more: 256 x 256 tiles on CTA pairs (cta_group::2), with edges
-# that are no multiple of the tile in every direction
+# the last four have 512 tokens or more: tiles of 256 x 256 or 256 x 192 on CTA pairs (cta_group::2;
+# the width that makes the waves of tiles shallower), with edges that are no multiple of the tile
+# in any direction; the last one has several waves of the narrower tile
 TC_SHAPES = [(1, 130, 96), (8, 3072, 2048), (17, 544, 96), (64, 391, 272), (65, 391, 272), (300, 130, 104),
-             (200, 1000, 72), (128, 256, 64), (5, 16, 8), (512, 512, 256), (1000, 4000, 520), (777, 264, 72)]
+             (200, 1000, 72), (128, 256, 64), (5, 16, 8), (512, 512, 256), (1000, 4000, 520), (777, 264, 72),
+             (2040, 3080, 136)]
 
 
 @pytest.mark.parametrize("epi", ["bf16", "f32", "silu", "residual"])
