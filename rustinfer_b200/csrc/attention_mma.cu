@@ -507,6 +507,7 @@ __device__ __forceinline__ bool tbar_try_wait(uint64_t* bar, unsigned parity) {
 }
 // bounded: false after T_SPIN_LIMIT tries, with 21 in *error
 __device__ __forceinline__ bool tbar_wait(uint64_t* bar, unsigned parity, int* error) {
+#pragma unroll 1
     for (unsigned i = 0; i < T_SPIN_LIMIT; ++i) {
         if (tbar_try_wait(bar, parity)) return true;
         if (i > 1024) __nanosleep(64);

@@ -74,6 +74,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* error, int code) {
+#pragma unroll 1
     for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 1024) __nanosleep(64);

@@ -105,6 +105,7 @@ __device__ __forceinline__ void tmem_ld4(unsigned addr, float (&v)[4]) {
 
 // All CTAs have arrived `target` times in total.  One thread spins (bounded).
 __device__ __forceinline__ bool grid_wait(const unsigned* bar, unsigned target, int* error) {
+#pragma unroll 1
     for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
         if (ld_acquire(bar) >= target) return true;
         if (i > 64) __nanosleep(32);
@@ -223,6 +224,7 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
             for (int s = 0; s < STAGES; ++s)
                 for (int par = 0; par < 2; ++par)
                     if (mbar_try_wait(&full[s], par)) break;
+#pragma unroll 1
             for (unsigned spin = 0; spin < 4096; ++spin) __nanosleep(256);
         }
     } else if (warp >= 2) {
@@ -336,46 +338,44 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                 tc_fence_after();
                 const int fl = quarter * 32 + lane;
                 const int feat = fl < P.a_box ? tile * P.a_box + fl : 0x3fffffff;
-                // The product's numbers go into registers first: read through `P` inside the loops
-                // they are fetched from the parameter bank again after every asm statement, which
-                // made a token cost 270 cycles.
+                // The lane's whole row (one feature, every token) comes out of tensor memory in one
+                // round trip.  The product's numbers go into registers first: read through `P`
+                // inside the loops they are fetched from the parameter bank again after every asm
+                // statement, which made a token cost 270 cycles.
                 const int out_kind = P.out_kind, ld_out = P.ld_out;
                 const bool scaled = P.x_kind == X_NORM, live = feat < P.N;
-                if (out_kind == OUT_ADD_F32) {
-                    float* o = reinterpret_cast<float*>(P.out) + (live ? feat : 0);
-                    for (int c0 = 0; c0 < M && ok; c0 += 4) {
-                        float v[4];
-                        tmem_ld4(taddr + c0, v);
+                void* const out = P.out;
+                float v[16];
+                static_assert(BN == 16, "the epilogue reads 16 columns");
+                if (ok) {
+                    tmem_ld16(taddr, v);
+                    if (scaled) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int tok = c0 + j;
-                            const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
-                            if (tok < M && live) atomicAdd(o + (size_t)tok * ld_out, a);
-                        }
+                        for (int j = 0; j < 16; ++j) v[j] *= row_scale[j];
                     }
-                } else if (out_kind == OUT_BF16) {
-                    bf16* o = reinterpret_cast<bf16*>(P.out) + (live ? feat : 0);
-                    for (int c0 = 0; c0 < M && ok; c0 += 4) {
-                        float v[4];
-                        tmem_ld4(taddr + c0, v);
+                    if (out_kind == OUT_ADD_F32) {
+                        float* o = reinterpret_cast<float*>(out) + (live ? feat : 0);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int tok = c0 + j;
-                            const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
-                            if (tok < M && live) o[(size_t)tok * ld_out] = __float2bfloat16_rn(a);
-                        }
-                    }
-                } else {
-                    bf16* o = reinterpret_cast<bf16*>(P.out) + (live ? (feat >> 1) : 0);
-                    for (int c0 = 0; c0 < M && ok; c0 += 4) {
-                        float v[4];
-                        tmem_ld4(taddr + c0, v);
+                        for (int j = 0; j < 16; ++j)
+                            if (j < M && live) atomicAdd(o + (size_t)j * ld_out, v[j]);
+                    } else if (out_kind == OUT_BF16) {
+                        bf16* o = reinterpret_cast<bf16*>(out) + (live ? feat : 0);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int tok = c0 + j;
-                            const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
-                            const float up = __shfl_xor_sync(0xffffffffu, a, 1);   // even lane gate, odd lane up
-                            if (tok < M && live && (lane & 1) == 0) o[(size_t)tok * ld_out] = __float2bfloat16_rn(silu_mul(a, up));
+                        for (int j = 0; j < 16; ++j)
+                            if (j < M && live) o[(size_t)j * ld_out] = __float2bfloat16_rn(v[j]);
+                    } else {
+                        // rows of the weight alternate gate_j, up_j: an even lane holds the gate and
+                        // its neighbour the up value of the same feature.  Of two tokens the even
+                        // lane finishes the first and the odd lane the second, so every lane does
+                        // one SiLU and one store per pair after one exchange.
+                        bf16* o = reinterpret_cast<bf16*>(out) + (live ? (feat >> 1) : 0);
+                        const bool odd = (lane & 1) != 0;
+#pragma unroll
+                        for (int j = 0; j < 16; j += 2) {
+                            const float got = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[j + 1], 1);
+                            const float g = odd ? got : v[j], u = odd ? v[j + 1] : got;
+                            const int tok = j + (odd ? 1 : 0);
+                            if (tok < M && live) o[(size_t)tok * ld_out] = __float2bfloat16_rn(silu_mul(g, u));
                         }
                     }
                 }
@@ -578,5 +578,5 @@ RI_API int ri_decode_chain(const RiChainPhase* phases, int n_phases, const RiCha
     }
     const size_t smem = 1024 + (size_t)p.nw_off + L.nw_bytes;
     cudaStream_t s = (cudaStream_t)stream;
-    return L.bn == 16 ? launch_chain<16>(maps, p, sms, smem, s) : launch_chain<32>(maps, p, sms, smem, s);
+    return launch_chain<16>(maps, p, sms, smem, s);
 }

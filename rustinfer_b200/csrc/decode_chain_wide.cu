@@ -72,6 +72,7 @@ __device__ __forceinline__ unsigned ld_acquire(const unsigned* p) {
     return v;
 }
 __device__ __forceinline__ bool grid_wait(const unsigned* bar, unsigned target, int* error) {
+#pragma unroll 1
     for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
         if (ld_acquire(bar) >= target) return true;
         if (i > 64) __nanosleep(32);
@@ -79,13 +80,28 @@ __device__ __forceinline__ bool grid_wait(const unsigned* bar, unsigned target, 
     atomicExch(error, ERR_WIDE_GRID);
     return false;
 }
-__device__ __forceinline__ void tmem_ld8(unsigned addr, float (&v)[8]) {
-    unsigned r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(addr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+// a lane's whole row of the accumulator in one round trip to tensor memory
+template <int N>
+__device__ __forceinline__ void tmem_ld_row(unsigned addr, float (&v)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld_row<32>(unsigned addr, float (&v)[32]) {
+    unsigned r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\t"
+                 "tcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(addr) : "memory");
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <>
+__device__ __forceinline__ void tmem_ld_row<64>(unsigned addr, float (&v)[64]) {
+    unsigned r[64];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n\t"
+                 "tcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+                 : "r"(addr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // Where a CTA is in its list of (product, item, stage): products only, conversions are skipped.
@@ -233,6 +249,7 @@ decode_chain_wide_kernel(const __grid_constant__ Maps maps, const __grid_constan
             for (int st = 0; st < STAGES; ++st)
                 for (int q = 0; q < 2; ++q)
                     if (mbar_try_wait(&full[st], q)) break;
+#pragma unroll 1
             for (unsigned spin = 0; spin < 4096; ++spin) __nanosleep(256);
         }
     } else if (warp >= 2) {
@@ -294,7 +311,7 @@ decode_chain_wide_kernel(const __grid_constant__ Maps maps, const __grid_constan
                 }
             } else {
                 if (P.rowsq) {
-                    if (te < M) row_scale[te] = 1.0f / sqrtf(__ldcg(P.rowsq + te) / (float)P.K + P.eps);
+                    if (te < BN) row_scale[te] = te < M ? 1.0f / sqrtf(__ldcg(P.rowsq + te) / (float)P.K + P.eps) : 0.f;
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                 }
                 for (int item = blockIdx.x; item < P.tiles * P.splits; item += G, ++n) {
@@ -304,50 +321,49 @@ decode_chain_wide_kernel(const __grid_constant__ Maps maps, const __grid_constan
                     tc_fence_after();
                     const int fl = quarter * 32 + lane;
                     const int feat = fl < P.a_box ? tile * P.a_box + fl : 0x3fffffff;
-                    // the product's numbers in registers: the loops below run once per eight tokens
+                    // The lane's whole row (one feature, every token) comes out of tensor memory in one
+                    // round trip, and the accumulator is given back before anything is stored: eight
+                    // round trips of eight tokens each were most of a 3 us epilogue.  The product's
+                    // numbers go into registers first (read through `P` they are fetched from the
+                    // parameter bank again after every asm statement).
                     const int out_kind = P.out_kind, ld_out = P.ld_out, n_feat = P.N;
                     const bool scaled = P.rowsq != nullptr, live = feat < n_feat;
-                    if (out_kind == OUT_ADD_F32) {
-                        float* o = reinterpret_cast<float*>(P.out) + (live ? feat : 0);
-                        for (int c0 = 0; c0 < M && ok; c0 += 8) {
-                            float v[8];
-                            tmem_ld8(taddr + c0, v);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int tok = c0 + j;
-                                const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
-                                if (tok < M && live) atomicAdd(o + (size_t)tok * ld_out, a);
-                            }
-                        }
-                    } else if (out_kind == OUT_BF16) {
-                        bf16* o = reinterpret_cast<bf16*>(P.out) + (live ? feat : 0);
-                        for (int c0 = 0; c0 < M && ok; c0 += 8) {
-                            float v[8];
-                            tmem_ld8(taddr + c0, v);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int tok = c0 + j;
-                                const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
-                                if (tok < M && live) o[(size_t)tok * ld_out] = __float2bfloat16_rn(a);
-                            }
-                        }
-                    } else {
-                        bf16* o = reinterpret_cast<bf16*>(P.out) + (live ? (feat >> 1) : 0);
-                        for (int c0 = 0; c0 < M && ok; c0 += 8) {
-                            float v[8];
-                            tmem_ld8(taddr + c0, v);
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const int tok = c0 + j;
-                                const float a = scaled ? v[j] * row_scale[min(tok, BN - 1)] : v[j];
-                                const float up = __shfl_xor_sync(0xffffffffu, a, 1);   // even lane gate, odd lane up
-                                if (tok < M && live && (lane & 1) == 0) o[(size_t)tok * ld_out] = __float2bfloat16_rn(silu_mul(a, up));
-                            }
-                        }
-                    }
+                    void* const out = P.out;
+                    float v[BN];
+                    if (ok) tmem_ld_row<BN>(taddr, v);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0 && ok) mbar_arrive(acc_empty);
+                    if (!ok) continue;
+                    if (scaled) {
+#pragma unroll
+                        for (int j = 0; j < BN; ++j) v[j] *= row_scale[j];
+                    }
+                    if (out_kind == OUT_ADD_F32) {
+                        float* o = reinterpret_cast<float*>(out) + (live ? feat : 0);
+#pragma unroll
+                        for (int j = 0; j < BN; ++j)
+                            if (j < M && live) atomicAdd(o + (size_t)j * ld_out, v[j]);
+                    } else if (out_kind == OUT_BF16) {
+                        bf16* o = reinterpret_cast<bf16*>(out) + (live ? feat : 0);
+#pragma unroll
+                        for (int j = 0; j < BN; ++j)
+                            if (j < M && live) o[(size_t)j * ld_out] = __float2bfloat16_rn(v[j]);
+                    } else {
+                        // rows of the weight alternate gate_j, up_j: an even lane holds the gate and its
+                        // neighbour the up value of the same feature.  Of two tokens the even lane
+                        // finishes the first and the odd lane the second, so every lane does one
+                        // SiLU and one store per pair after one exchange.
+                        bf16* o = reinterpret_cast<bf16*>(out) + (live ? (feat >> 1) : 0);
+                        const bool odd = (lane & 1) != 0;
+#pragma unroll
+                        for (int j = 0; j < BN; j += 2) {
+                            const float got = __shfl_xor_sync(0xffffffffu, odd ? v[j] : v[j + 1], 1);
+                            const float g = odd ? got : v[j], u = odd ? v[j + 1] : got;
+                            const int tok = j + (odd ? 1 : 0);
+                            if (tok < M && live) o[(size_t)tok * ld_out] = __float2bfloat16_rn(silu_mul(g, u));
+                        }
+                    }
                 }
             }
             __threadfence();
@@ -359,40 +375,69 @@ decode_chain_wide_kernel(const __grid_constant__ Maps maps, const __grid_constan
             if (threadIdx.x == 64 && *go_slot && !grid_wait(p.grid_bar, (unsigned)G * p.n_phases, p.error)) *go_slot = 0;
             asm volatile("bar.sync 1, 128;" ::: "memory");
             ok = ok && *go_slot;
+            // A warp takes a run of consecutive (token, head) rows, four at a time: first the
+            // positions of all four, then their angles and values (loads that do not wait for one
+            // another), then the arithmetic and the stores.  One row at a time the three dependent
+            // round trips of each row added up to 6 us at 64 tokens.
             const int heads = R.Hq + 2 * R.Hkv, half = R.rot >> 1;
             const size_t head_step = (size_t)R.page_size * R.hd;
-            for (int wi = blockIdx.x * 4 + quarter; wi < M * heads && ok; wi += G * 4) {
-                const int t = wi / heads, hh = wi - t * heads;
-                float* src = R.qkv + (size_t)t * R.ld + (size_t)hh * R.hd;
-                const int slot = R.slot_of_token ? R.slot_of_token[t] : -1;
-                bf16* dst = nullptr;
-                if (hh < R.Hq) {
-                    dst = R.q_out + (size_t)t * R.ld_q + (size_t)hh * R.hd;
-                } else if (slot >= 0 && R.cache) {
-                    const int page = slot / R.page_size, off = slot - page * R.page_size;
-                    const int kv = hh < R.Hq + R.Hkv ? 0 : 1, g = hh - R.Hq - kv * R.Hkv;
-                    dst = R.cache + ((size_t)(page * 2 + kv) * R.Hkv * R.page_size + off) * R.hd + (size_t)g * head_step;
+            const int rows = M * heads, warps = G * 4, per = (rows + warps - 1) / warps;
+            const int first = (blockIdx.x * 4 + quarter) * per, last = min(first + per, rows);
+            constexpr int RB = 4, JMAX = 4;                       // rows at a time; 32-lane strides of half a head
+            if (half > 32 * JMAX && ok) { atomicExch(p.error, ERR_WIDE_EPILOGUE); ok = false; }
+            for (int r0 = first; r0 < last && ok; r0 += RB) {
+                int tok[RB], hh[RB], pos[RB];
+#pragma unroll
+                for (int b = 0; b < RB; ++b) {
+                    const int wi = min(r0 + b, last - 1);
+                    tok[b] = wi / heads;
+                    hh[b] = wi - tok[b] * heads;
+                    pos[b] = hh[b] < R.Hq + R.Hkv ? R.positions[tok[b]] : 0;
                 }
-                if (hh < R.Hq + R.Hkv) {
-                    const int pos = R.positions[t];
-                    const float* ct = R.cos_t + (size_t)pos * half;
-                    const float* st = R.sin_t + (size_t)pos * half;
-                    for (int j = lane; j < half; j += 32) {
-                        const float x1 = __ldcg(src + j), x2 = __ldcg(src + j + half);
-                        const float c = ct[j], s = st[j];
-                        if (dst) {
-                            dst[j] = __float2bfloat16_rn(x1 * c - x2 * s);
-                            dst[j + half] = __float2bfloat16_rn(x1 * s + x2 * c);
-                        }
+                float x1[RB][JMAX], x2[RB][JMAX], cs[RB][JMAX], sn[RB][JMAX];
+#pragma unroll
+                for (int b = 0; b < RB; ++b) {
+                    const float* src = R.qkv + (size_t)tok[b] * R.ld + (size_t)hh[b] * R.hd;
+                    const bool rotated = hh[b] < R.Hq + R.Hkv;
+                    const float* ct = R.cos_t + (size_t)pos[b] * half;
+                    const float* st = R.sin_t + (size_t)pos[b] * half;
+#pragma unroll
+                    for (int jj = 0; jj < JMAX; ++jj) {
+                        const int j = jj * 32 + lane;
+                        const bool in = j < half;
+                        x1[b][jj] = in ? __ldcg(src + j) : 0.f;
+                        x2[b][jj] = in ? __ldcg(src + j + half) : 0.f;
+                        cs[b][jj] = in && rotated ? ct[j] : 1.f;
+                        sn[b][jj] = in && rotated ? st[j] : 0.f;
                     }
+                }
+#pragma unroll
+                for (int b = 0; b < RB; ++b) {
+                    if (r0 + b >= last) continue;
+                    float* src = R.qkv + (size_t)tok[b] * R.ld + (size_t)hh[b] * R.hd;
+                    const int slot = R.slot_of_token ? R.slot_of_token[tok[b]] : -1;
+                    bf16* dst = nullptr;
+                    if (hh[b] < R.Hq) {
+                        dst = R.q_out + (size_t)tok[b] * R.ld_q + (size_t)hh[b] * R.hd;
+                    } else if (slot >= 0 && R.cache) {
+                        const int page = slot / R.page_size, off = slot - page * R.page_size;
+                        const int kv = hh[b] < R.Hq + R.Hkv ? 0 : 1, g = hh[b] - R.Hq - kv * R.Hkv;
+                        dst = R.cache + ((size_t)(page * 2 + kv) * R.Hkv * R.page_size + off) * R.hd + (size_t)g * head_step;
+                    }
+                    // values (cos 1, sin 0) and the columns beyond the rotated ones pass unchanged
                     for (int j = R.rot + lane; j < R.hd; j += 32)
                         if (dst) dst[j] = __float2bfloat16_rn(__ldcg(src + j));
-                } else {
-                    for (int j = lane; j < R.hd; j += 32)
-                        if (dst) dst[j] = __float2bfloat16_rn(__ldcg(src + j));
+#pragma unroll
+                    for (int jj = 0; jj < JMAX; ++jj) {
+                        const int j = jj * 32 + lane;
+                        if (j < half && dst) {
+                            dst[j] = __float2bfloat16_rn(x1[b][jj] * cs[b][jj] - x2[b][jj] * sn[b][jj]);
+                            dst[j + half] = __float2bfloat16_rn(x1[b][jj] * sn[b][jj] + x2[b][jj] * cs[b][jj]);
+                        }
+                    }
+                    __syncwarp();
+                    for (int j = lane; j < R.hd; j += 32) src[j] = 0.f;
                 }
-                __syncwarp();
-                for (int j = lane; j < R.hd; j += 32) src[j] = 0.f;
             }
         }
     }

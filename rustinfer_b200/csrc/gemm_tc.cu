@@ -257,6 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int s = 0; s < STAGES; ++s)
                 for (int par = 0; par < 2; ++par)
                     if (mbar_try_wait(&full[s], par)) break;
+#pragma unroll 1
             for (unsigned spin = 0; spin < 4096; ++spin) __nanosleep(256);
         }
     } else if (warp >= 2) {
@@ -271,7 +272,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // lanes beyond the rows this tile loaded hold nothing of this tile
             const int ra = quarter * 32 + lane < p.a_box ? a0 + quarter * 32 + lane : 0x3fffffff;
             const int buf = t & 1, use = t >> 1;
-            if (ok && n_kb > 0) ok = mbar_wait(&acc_full[buf], use & 1, p.error, ERR_EPILOGUE_WAIT);
+            // (also for a K slice that got no k-block: the MMA thread commits at once, but it must
+            // have passed its own wait on `acc_empty` before these warps arrive there, or it would
+            // wait for a phase that never comes)
+            if (ok) ok = mbar_wait(&acc_full[buf], use & 1, p.error, ERR_EPILOGUE_WAIT);
             tc_fence_after();
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + buf * C::ACC_COLS;
             const bool have = ok && n_kb > 0;
@@ -546,6 +550,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int st = 0; st < STAGES; ++st)
                 for (int q = 0; q < 2; ++q)
                     if (mbar_try_wait(&full[st], q)) break;
+#pragma unroll 1
             for (unsigned spin = 0; spin < 4096; ++spin) __nanosleep(256);
         }
     } else if (warp >= 2) {

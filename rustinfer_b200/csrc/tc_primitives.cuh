@@ -28,7 +28,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
     return ok != 0;
 }
 // Bounded wait: false after SPIN_LIMIT tries (about a tenth of a second), with `code` in *error.
+// (the loop is kept rolled: unrolled, each of the many places that wait grew by 4 KB of
+// instructions, and kernels of 140 KB ran their one-time code out of the instruction cache)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* error, int code) {
+#pragma unroll 1
     for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (i > 1024) __nanosleep(64);
@@ -84,5 +87,7 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
     return r;
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+// the quotient by the fast reciprocal (2 ulp; 0 for a denominator beyond 2^126, the limit of the function): the
+// IEEE division cost the few-token epilogues a third of their time and the result is rounded to bf16 anyway
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 }  // namespace ri_tc
