@@ -140,6 +140,46 @@ __device__ __forceinline__ void store_row16(const Params& p, int tok, int feat0,
 }
 
 
+// 64 consecutive features of one token, all inside the matrix and with rows that allow vector
+// stores (the caller has checked both for the whole warp)
+__device__ __forceinline__ void store_row64(const Params& p, int tok, int feat0, const float (&v)[64]) {
+    if (tok >= p.a_rows) return;
+    const size_t row = (size_t)tok * p.ld_out;
+    switch (p.epilogue) {
+        case EPI_BF16: {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + feat0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = pack8(v + 8 * j);
+            break;
+        }
+        case EPI_F32: {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + row + feat0);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            break;
+        }
+        case EPI_RESIDUAL: {
+            float* dst = reinterpret_cast<float*>(p.out) + row + feat0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                             ::"l"(dst + 4 * j), "f"(v[4 * j]), "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+            break;
+        }
+        case EPI_SILU: {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + row + (feat0 >> 1));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float m[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) m[j] = silu_mul(v[16 * q + 2 * j], v[16 * q + 2 * j + 1]);
+                dst[q] = pack8(m);
+            }
+            break;
+        }
+    }
+}
+
 // Persistent over tiles: CTA x takes tiles x, x + gridDim.x, ...; blockIdx.z is the K slice.
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 2)
@@ -567,10 +607,23 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + buf * ACC_COLS;
             if (ok) {
-                for (int c0 = 0; c0 < BN; c0 += 16) {
-                    float v[16];
-                    tmem_ld16(taddr + c0, v);
-                    store_row16(p, ra, b0 + c0, v);
+                // 64 columns a round trip to tensor memory where the tile lies inside the matrix
+                // (the width is 192 or 256): the epilogue of a pair's last tile has no MMA to hide
+                // behind.  At the ragged edge 16 at a time, element by element.
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    if (p.vec && b0 + c0 + 64 <= p.b_rows) {
+                        float v[64];
+                        tmem_ld_row<64>(taddr + c0, v);
+                        store_row64(p, ra, b0 + c0, v);
+                    } else {
+#pragma unroll 1
+                        for (int c1 = c0; c1 < c0 + 64; c1 += 16) {
+                            float v[16];
+                            tmem_ld16(taddr + c1, v);
+                            store_row16(p, ra, b0 + c1, v);
+                        }
+                    }
                 }
             }
             tc_fence_before();
