@@ -287,16 +287,26 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                         nw_here = true;
                         ok = mbar_wait(x_land, xl & 1, p.error, ERR_CHAIN_EPILOGUE);
                         ++xl;
-                        for (int r = quarter; r < rows && ok; r += 4) {
-                            const float* row = stg + (size_t)r * Kc;
-                            const int rr = r0 + r;
-                            float ss = 0.f;
+                        // a warp norms rows quarter, quarter + 4, ... two at a time: the norm weight is
+                        // read and widened once for both, and the loads of one row do not wait for the
+                        // arithmetic of the other
+                        for (int r = quarter; r < rows && ok; r += 8) {
+                            const bool two = r + 4 < rows;
+                            const float* row_a = stg + (size_t)r * Kc;
+                            const float* row_b = stg + (size_t)(two ? r + 4 : r) * Kc;
+                            const int ra = r0 + r, rb = ra + 4;
+                            float ss_a = 0.f, ss_b = 0.f;
+#pragma unroll 2
                             for (int u = lane; u < upr; u += 32) {
                                 const int k = u * 8;
-                                const float4 x0 = *reinterpret_cast<const float4*>(row + k);
-                                const float4 x1 = *reinterpret_cast<const float4*>(row + k + 4);
-                                ss += x0.x * x0.x + x0.y * x0.y + x0.z * x0.z + x0.w * x0.w
-                                    + x1.x * x1.x + x1.y * x1.y + x1.z * x1.z + x1.w * x1.w;
+                                const float4 a0 = *reinterpret_cast<const float4*>(row_a + k);
+                                const float4 a1 = *reinterpret_cast<const float4*>(row_a + k + 4);
+                                const float4 b0 = *reinterpret_cast<const float4*>(row_b + k);
+                                const float4 b1 = *reinterpret_cast<const float4*>(row_b + k + 4);
+                                ss_a += (a0.x * a0.x + a0.y * a0.y) + (a0.z * a0.z + a0.w * a0.w)
+                                      + (a1.x * a1.x + a1.y * a1.y) + (a1.z * a1.z + a1.w * a1.w);
+                                ss_b += (b0.x * b0.x + b0.y * b0.y) + (b0.z * b0.z + b0.w * b0.w)
+                                      + (b1.x * b1.x + b1.y * b1.y) + (b1.z * b1.z + b1.w * b1.w);
                                 if (k >= k_lo && k < k_hi) {
                                     float w[8];
                                     if (nw_bf16) {
@@ -312,14 +322,24 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                                         const float4 wb = *reinterpret_cast<const float4*>(nws + (size_t)k * 4 + 16);
                                         w[0] = wa.x; w[1] = wa.y; w[2] = wa.z; w[3] = wa.w; w[4] = wb.x; w[5] = wb.y; w[6] = wb.z; w[7] = wb.w;
                                     }
+                                    unsigned char* dst = xs + (size_t)((k >> 6) - kb0) * x_kb_bytes;
                                     float x[8];
-                                    x[0] = x0.x * w[0]; x[1] = x0.y * w[1]; x[2] = x0.z * w[2]; x[3] = x0.w * w[3];
-                                    x[4] = x1.x * w[4]; x[5] = x1.y * w[5]; x[6] = x1.z * w[6]; x[7] = x1.w * w[7];
-                                    *reinterpret_cast<uint4*>(xs + (size_t)((k >> 6) - kb0) * x_kb_bytes + rr * 128 + (((u & 7) ^ (rr & 7)) << 4)) = pack8(x);
+                                    x[0] = a0.x * w[0]; x[1] = a0.y * w[1]; x[2] = a0.z * w[2]; x[3] = a0.w * w[3];
+                                    x[4] = a1.x * w[4]; x[5] = a1.y * w[5]; x[6] = a1.z * w[6]; x[7] = a1.w * w[7];
+                                    *reinterpret_cast<uint4*>(dst + ra * 128 + (((u & 7) ^ (ra & 7)) << 4)) = pack8(x);
+                                    if (two) {
+                                        x[0] = b0.x * w[0]; x[1] = b0.y * w[1]; x[2] = b0.z * w[2]; x[3] = b0.w * w[3];
+                                        x[4] = b1.x * w[4]; x[5] = b1.y * w[5]; x[6] = b1.z * w[6]; x[7] = b1.w * w[7];
+                                        *reinterpret_cast<uint4*>(dst + rb * 128 + (((u & 7) ^ (rb & 7)) << 4)) = pack8(x);
+                                    }
                                 }
                             }
-                            ss = warp_sum(ss);
-                            if (lane == 0) row_scale[rr] = 1.0f / sqrtf(ss / (float)Kc + eps);
+                            ss_a = warp_sum(ss_a);
+                            ss_b = warp_sum(ss_b);
+                            if (lane == 0) {
+                                row_scale[ra] = rsqrtf(ss_a / (float)Kc + eps);
+                                if (two) row_scale[rb] = rsqrtf(ss_b / (float)Kc + eps);
+                            }
                         }
                         // the staged rows may be overwritten, the scales are there for all warps
                         asm volatile("bar.sync 1, 128;" ::: "memory");
