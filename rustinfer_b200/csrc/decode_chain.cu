@@ -410,15 +410,30 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
         if (p.rope.enabled) {
             // ---------------- rotary encoding of q and k, keys and values into their pages
             const Rope& R = p.rope;
+            const int heads = R.Hq + 2 * R.Hkv, half = R.rot >> 1;
+            const size_t head_step = (size_t)R.page_size * R.hd;
+            // What the warp's first row needs besides the product (its position, its place in the
+            // cache, its angles) is fetched before the wait for the product: two trips to L2 that
+            // run beside the barrier instead of after it.
+            const int wi0 = blockIdx.x * 4 + quarter;
+            int t0 = 0, slot0 = -1, pos0 = 0;
+            float c0 = 1.f, s0 = 0.f;
+            if (wi0 < M * heads) {
+                t0 = wi0 / heads;
+                slot0 = R.slot_of_token ? R.slot_of_token[t0] : -1;
+                if (wi0 - t0 * heads < R.Hq + R.Hkv) {
+                    pos0 = R.positions[t0];
+                    if (lane < half) { c0 = R.cos_t[(size_t)pos0 * half + lane]; s0 = R.sin_t[(size_t)pos0 * half + lane]; }
+                }
+            }
             if (threadIdx.x == 64 && *go_slot && !grid_wait(p.grid_bar, (unsigned)G * p.n_phases, p.error)) *go_slot = 0;
             asm volatile("bar.sync 1, 128;" ::: "memory");
             ok = ok && *go_slot;
-            const int heads = R.Hq + 2 * R.Hkv, half = R.rot >> 1;
-            const size_t head_step = (size_t)R.page_size * R.hd;
-            for (int wi = blockIdx.x * 4 + quarter; wi < M * heads && ok; wi += G * 4) {
-                const int t = wi / heads, hh = wi - t * heads;
+            for (int wi = wi0; wi < M * heads && ok; wi += G * 4) {
+                const bool first = wi == wi0;
+                const int t = first ? t0 : wi / heads, hh = wi - t * heads;
                 float* src = R.qkv + (size_t)t * R.ld + (size_t)hh * R.hd;
-                const int slot = R.slot_of_token ? R.slot_of_token[t] : -1;
+                const int slot = first ? slot0 : (R.slot_of_token ? R.slot_of_token[t] : -1);
                 bf16* dst = nullptr;
                 if (hh < R.Hq) {
                     dst = R.q_out + (size_t)t * R.ld_q + (size_t)hh * R.hd;
@@ -428,12 +443,13 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                     dst = R.cache + ((size_t)(page * 2 + kv) * R.Hkv * R.page_size + off) * R.hd + (size_t)g * head_step;
                 }
                 if (hh < R.Hq + R.Hkv) {
-                    const int pos = R.positions[t];
+                    const int pos = first ? pos0 : R.positions[t];
                     const float* ct = R.cos_t + (size_t)pos * half;
                     const float* st = R.sin_t + (size_t)pos * half;
                     for (int j = lane; j < half; j += 32) {
                         const float x1 = __ldcg(src + j), x2 = __ldcg(src + j + half);
-                        const float c = ct[j], s = st[j];
+                        const bool have = first && j == lane;
+                        const float c = have ? c0 : ct[j], s = have ? s0 : st[j];
                         if (dst) {
                             dst[j] = __float2bfloat16_rn(x1 * c - x2 * s);
                             dst[j + half] = __float2bfloat16_rn(x1 * s + x2 * c);
