@@ -532,8 +532,11 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
                   const int* __restrict__ entry_list, int Hq, int Hkv, int Gc, int chunks, int page_size, int box_rows,
                   float scale_log2, int window, int splits, float* __restrict__ part_o,
                   float* __restrict__ part_lse, int* __restrict__ error) {
+    // The kernel before this one (rotary encoding and cache write, alone or at the end of a chain)
+    // writes q and the keys and values of this step's tokens only; what the step was told
+    // (entries, lengths, block table) and every earlier key were written before it began.  So
+    // only the loads of q and of the tile that holds the newest key wait for it.
     pdl_trigger();
-    pdl_wait();
     extern __shared__ unsigned char smem_raw[];
     unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     bf16* Qs = reinterpret_cast<bf16*>(ring + (size_t)TSTAGES * T_STAGE_BYTES);    // [16][ROW]
@@ -556,11 +559,12 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
     const int t_begin = t_first + split * per, t_end = min(t_begin + per, t_first + t_count);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    if (tid == 0) {
+    if (tid == DWARPS * 32) {                              // the producer: its first tiles go out before the others are ready
         for (int s = 0; s < TSTAGES; ++s) { tbar_init(&full[s], 1); tbar_init(&empty[s], DWARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid < DTHREADS) {
+        pdl_wait();
         for (int c = tid; c < 16 * CH; c += DTHREADS) {
             const int r = c / CH, ch = c - r * CH;
             uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -569,6 +573,58 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
             *reinterpret_cast<uint4*>(Qs + r * ROW + ch * 8) = v;
         }
     }
+    // ------------------------------------------------------------------------ TMA producer
+    // One thread, lean on purpose (it paces the CTA): no division in the loop, page numbers
+    // read one tile ahead.  Pages past the request's last one are never allocated: its first
+    // page is read instead (those keys are masked, their V rows zeroed before use).  Its first
+    // tiles go out before the other warps have q.
+    const bool producer = tid == DWARPS * 32;
+    const int* bt = block_table + (size_t)b * table_stride;
+    const int boxes = DKT / box_rows;                      // at most 8 pages meet a tile
+    const bool small_pages = page_size < DKT;
+    const int kv_step = Hkv * page_size;
+    const int t_newest = t_first + t_count - 1;            // the tile with this step's key
+    int blk = (t_begin * DKT) / page_size, off = small_pages ? 0 : (t_begin * DKT) % page_size;
+    int pages[8], pages_next[8];
+    auto look_up = [&](int key0, int blk0, bool live, int (&dst)[8]) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            dst[c] = (live && c < boxes) ? bt[key0 + c * box_rows < kvl ? blk0 + c : 0] : 0;
+    };
+    bool p_ok = true, waited = false;
+    int p_s = 0;
+    unsigned p_par = 1;
+    auto issue = [&](int t) {
+        const int key0 = t * DKT;
+        int blk_n = blk, off_n = off;
+        if (small_pages) blk_n += boxes;
+        else if ((off_n += DKT) >= page_size) { off_n = 0; ++blk_n; }
+        look_up(key0 + DKT, blk_n, t + 1 < t_end, pages_next);
+        if (t - t_begin >= TSTAGES && !tbar_try_wait(&empty[p_s], p_par) && !tbar_wait(&empty[p_s], p_par, error)) { p_ok = false; return; }
+        if (t >= t_newest && !waited) { pdl_wait(); waited = true; }
+        unsigned char* dst = ring + (size_t)p_s * T_STAGE_BYTES;
+        tbar_expect_tx(&full[p_s], T_STAGE_BYTES);
+#pragma unroll
+        for (int kv = 0; kv < 2; ++kv)
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                if (c < boxes) {
+                    const int row = (pages[c] * 2 * Hkv + kvh) * page_size + kv * kv_step + (key0 + c * box_rows < kvl ? off : 0);
+#pragma unroll
+                    for (int kb = 0; kb < TKB; ++kb)
+                        t_tma_load_2d(dst + kv * T_TILE_BYTES + kb * (DKT * 128) + c * box_rows * 128, &cache_map, &full[p_s], kb * 64, row);
+                }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) pages[c] = pages_next[c];
+        blk = blk_n; off = off_n;
+        if (++p_s == TSTAGES) { p_s = 0; p_par ^= 1u; }
+    };
+    const int t_early = min(t_end, t_begin + TSTAGES);
+    if (producer) {
+        look_up(t_begin * DKT, blk, t_begin < t_end, pages);
+        for (int t = t_begin; t < t_early && p_ok; ++t) issue(t);
+    }
+    __syncwarp();
     __syncthreads();
 
     float o[NT][4];
@@ -577,51 +633,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     if (warp == DWARPS) {
-        // ------------------------------------------------------------------ TMA producer
-        // Lean on purpose (this thread paces the CTA): no division in the loop, page numbers
-        // read one tile ahead.  Pages past the request's last one are never allocated: its
-        // first page is read instead (those keys are masked, their V rows zeroed before use).
-        if (lane == 0) {
-            const int* bt = block_table + (size_t)b * table_stride;
-            const int boxes = DKT / box_rows;                  // at most 8 pages meet a tile
-            const bool small_pages = page_size < DKT;
-            int blk = (t_begin * DKT) / page_size, off = small_pages ? 0 : (t_begin * DKT) % page_size;
-            int pages[8], pages_next[8];
-            auto look_up = [&](int key0, int blk0, bool live, int (&dst)[8]) {
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    dst[c] = (live && c < boxes) ? bt[key0 + c * box_rows < kvl ? blk0 + c : 0] : 0;
-            };
-            look_up(t_begin * DKT, blk, t_begin < t_end, pages);
-            const int kv_step = Hkv * page_size;
-            bool ok = true;
-            int s = 0;
-            unsigned par = 1;
-            for (int t = t_begin; t < t_end && ok; ++t) {
-                const int key0 = t * DKT;
-                int blk_n = blk, off_n = off;
-                if (small_pages) blk_n += boxes;
-                else if ((off_n += DKT) >= page_size) { off_n = 0; ++blk_n; }
-                look_up(key0 + DKT, blk_n, t + 1 < t_end, pages_next);
-                if (t - t_begin >= TSTAGES && !tbar_try_wait(&empty[s], par) && !tbar_wait(&empty[s], par, error)) { ok = false; break; }
-                unsigned char* dst = ring + (size_t)s * T_STAGE_BYTES;
-                tbar_expect_tx(&full[s], T_STAGE_BYTES);
-#pragma unroll
-                for (int kv = 0; kv < 2; ++kv)
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        if (c < boxes) {
-                            const int row = (pages[c] * 2 * Hkv + kvh) * page_size + kv * kv_step + (key0 + c * box_rows < kvl ? off : 0);
-#pragma unroll
-                            for (int kb = 0; kb < TKB; ++kb)
-                                t_tma_load_2d(dst + kv * T_TILE_BYTES + kb * (DKT * 128) + c * box_rows * 128, &cache_map, &full[s], kb * 64, row);
-                        }
-#pragma unroll
-                for (int c = 0; c < 8; ++c) pages[c] = pages_next[c];
-                blk = blk_n; off = off_n;
-                if (++s == TSTAGES) { s = 0; par ^= 1u; }
-            }
-        }
+        if (producer)
+            for (int t = t_early; t < t_end && p_ok; ++t) issue(t);
     } else {
         // ---------------------------------------------------------------------- the warps
         unsigned qf[KS][4];

@@ -208,8 +208,10 @@ __global__ void rope_scatter_kernel(TA* __restrict__ qkv, int row_stride,
                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                     const int* __restrict__ slot_of_token, TA* __restrict__ cache,
                                     int Hq, int Hkv, int hd, int rot, int page_size) {
-    pdl_trigger();
+    // wait first, then let the next kernel start: the attention kernel that follows reads all
+    // but this kernel's output before its own wait, so every earlier kernel must be complete by then
     pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int pos = positions[t];
@@ -263,8 +265,10 @@ __global__ void rope_scatter_bf16x8_kernel(bf16* __restrict__ qkv, int row_strid
                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                            const int* __restrict__ slot_of_token, bf16* __restrict__ cache,
                                            int Hq, int Hkv, int hd, int rot, int page_size) {
-    pdl_trigger();
+    // wait first, then let the next kernel start: the attention kernel that follows reads all
+    // but this kernel's output before its own wait, so every earlier kernel must be complete by then
     pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int pos = positions[t];
