@@ -775,12 +775,14 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
 __global__ void combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                bf16* __restrict__ out, int out_stride, const int* __restrict__ cu_q,
                                const int* __restrict__ entry_list, int Hq, int splits) {
+    // (which token this is was settled before the step's first kernel: read before the wait for
+    // the partial results)
     pdl_trigger();
-    pdl_wait();
     const int slot = blockIdx.x, head = blockIdx.y;
     const int b = entry_list ? entry_list[slot] : slot;
     if (b < 0) return;
     const int tok = cu_q[b + 1] - 1;
+    pdl_wait();
     const size_t p = ((size_t)slot * Hq + head) * splits;
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, part_lse[p + s]);
