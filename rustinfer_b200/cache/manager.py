@@ -63,6 +63,61 @@ class CacheLayout:
         return [i for i, g in enumerate(self.groups) if isinstance(g.need, PagedKV)]
 
 
+class Lease:
+    """Pages checked out for one step: `commit()` makes them the requests' own (and counts the
+    step's tokens), `release()` returns them to the pool and leaves every table as it was
+    before.  One of the two must be called; as a context manager the lease commits on a clean
+    exit and releases when the body raises.  RustInfer's `KvLease` is the same contract over
+    token slots (crates/infer-worker/src/domain/global_kv_alloc.rs:393-461); where its drop of
+    an unsettled lease asserts, this one gives the pages back and warns."""
+
+    def __init__(self, manager: "CacheManager", batch: List[Tuple[Any, int]], taken: List[Dict[int, int]]):
+        self._m, self._batch, self._taken = manager, batch, taken
+        self.settled = False
+
+    def _settle(self) -> None:
+        if self.settled:
+            raise RuntimeError("this lease was already committed or released")
+        self.settled = True
+
+    def commit(self) -> None:
+        self._settle()
+        for rid, n in self._batch:
+            self._m.commit(rid, n)
+
+    def release(self) -> None:
+        self._settle()
+        for (rid, _n), taken in zip(self._batch, self._taken):
+            r = self._m._req.get(rid)
+            if r is None:                                  # closed meanwhile: close() freed its pages
+                continue
+            for g, k in taken.items():
+                if k:
+                    table = r.tables[g]
+                    self._m.pools[g].free(table[len(table) - k:])
+                    del table[len(table) - k:]
+
+    def __enter__(self) -> "Lease":
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> bool:
+        if not self.settled:
+            if exc_type is None:
+                self.commit()
+            else:
+                self.release()
+        return False
+
+    def __del__(self):
+        if not getattr(self, "settled", True):
+            import warnings
+            warnings.warn("a cache lease was dropped unsettled; its pages are given back")
+            try:
+                self.release()
+            except Exception:
+                pass
+
+
 @dataclass
 class _Request:
     slot: int
@@ -138,8 +193,18 @@ class CacheManager:
     def free_pages(self) -> Dict[int, int]:
         return {g: p.free_count for g, p in self.pools.items()}
 
-    def reserve(self, batch: Sequence[Tuple[Any, int]]) -> None:
-        """Pages for every (request, new tokens) of a step, all or nothing."""
+    def lease(self, batch: Sequence[Tuple[Any, int]]) -> "Lease":
+        """`reserve` as a lease: the pages are checked out for the step and become the requests'
+        own when it commits; if the step fails they go back to the pool.  Use as
+
+            with cache.lease(batch):
+                run the step            # an exception gives the pages back and passes on
+        """
+        return Lease(self, list(batch), self.reserve(batch))
+
+    def reserve(self, batch: Sequence[Tuple[Any, int]]) -> List[Dict[int, int]]:
+        """Pages for every (request, new tokens) of a step, all or nothing.  Returns, per
+        entry of the batch, how many pages each group handed out."""
         total: Dict[int, int] = {g: 0 for g in self.pools}
         per: List[Dict[int, int]] = []
         for rid, n in batch:
@@ -155,6 +220,7 @@ class CacheManager:
             for g, k in need.items():
                 if k:
                     r.tables[g].extend(self.pools[g].alloc(k))
+        return per
 
     def commit(self, request_id: Any, new_tokens: int) -> None:
         """The step stored `new_tokens` tokens; pages a window has passed are given back."""

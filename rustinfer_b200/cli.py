@@ -20,12 +20,15 @@ def _run(path: str) -> int:
     from .config.run_config import RunConfig
     from .sampling.params import SamplingParams
     cfg = RunConfig.load(path)
+    scratch = None
     if cfg.random_weights:
         from .weights.random_init import write_random_model
         rw = cfg.random_weights
         with open(rw["config"]) as f:
             model_cfg = json.load(f)
-        cfg.model = cfg.model or tempfile.mkdtemp(prefix="rustinfer_b200_random_")
+        if not cfg.model:                                     # no place named: a folder that goes with the run
+            scratch = tempfile.TemporaryDirectory(prefix="rustinfer_b200_random_")
+            cfg.model = scratch.name
         write_random_model(cfg.model, model_cfg, int(rw.get("seed", 0)), float(rw.get("std", 0.02)),
                            float(rw.get("norm_std", 0.0)), str(rw.get("dtype", "bfloat16")))
     from .engine.engine import Engine
@@ -55,6 +58,8 @@ def _run(path: str) -> int:
     print(json.dumps({"steps": st.steps, "prompt_tokens": st.prompt_tokens,
                       "generated_tokens": st.generated_tokens, "preemptions": st.preemptions,
                       "seconds": round(st.seconds, 4)}), file=sys.stderr)
+    if scratch is not None:
+        scratch.cleanup()
     return 0
 
 

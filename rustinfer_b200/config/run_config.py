@@ -94,4 +94,8 @@ class RunConfig:
         base = os.path.dirname(os.path.abspath(path))
         if cfg.model and not os.path.isabs(cfg.model):
             cfg.model = os.path.normpath(os.path.join(base, cfg.model))
+        # paths in the run file are relative to the run file, not to where the program was started
+        rw = cfg.random_weights
+        if rw and rw.get("config") and not os.path.isabs(str(rw["config"])):
+            cfg.random_weights = dict(rw, config=os.path.normpath(os.path.join(base, str(rw["config"]))))
         return cfg

@@ -18,7 +18,8 @@
 //    cudaErrorInvalidValue and ri_attention_decode_static_error() tells why; nothing is
 //    launched.
 //  * The first call on a device looks up the array's device address and raises the
-//    kernels' shared-memory limit.  Make that first call outside any stream capture.
+//    kernels' shared-memory limit.  Make that first call outside any stream capture.  The
+//    look-up runs under a host lock, so host threads may race to be first.
 //  * The function calls no cudaMalloc, cudaFree or allocating library routine, on any call.
 //  * Every call uses the same array.  Two calls whose kernels may overlap on the GPU (other
 //    streams, other host threads) race on it; keep calls on one stream or order them

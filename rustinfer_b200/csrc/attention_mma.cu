@@ -650,12 +650,13 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
             unsigned char* Vt = ring + (size_t)s * T_STAGE_BYTES + T_TILE_BYTES;
             if (!tbar_try_wait(&full[s], par) && !tbar_wait(&full[s], par, error)) { ok = false; break; }
             if (t * DKT + kw0 < kvl) {
-                // value rows of keys past the end hold whatever the cache holds there: they meet
-                // probability zero, but zero times NaN is NaN, so they are cleared
-                if (t * DKT + kw0 + 16 > kvl) {
+                // value rows of keys past the end, or before the window (their pages may have been
+                // given back and belong to another request by now), hold whatever the cache holds
+                // there: they meet probability zero, but zero times NaN is NaN, so they are cleared
+                if (t * DKT + kw0 + 16 > kvl || t * DKT + kw0 < lo) {
                     for (int i = lane; i < 16 * TKB * 8; i += 32) {
                         const int r = kw0 + (i / (TKB * 8)), c8 = i % (TKB * 8);
-                        if (t * DKT + r >= kvl)
+                        if (t * DKT + r >= kvl || t * DKT + r < lo)
                             *reinterpret_cast<uint4*>(const_cast<unsigned char*>(swz(Vt, r, c8 * 8))) = make_uint4(0u, 0u, 0u, 0u);
                     }
                     __syncwarp();
@@ -976,6 +977,9 @@ float* g_decode_static_ptr[MAX_DEVICES] = {nullptr};
 thread_local char g_decode_static_msg[256] = "";
 
 int decode_static_setup(int device, float** ptr) {
+    // two host threads may make a device's first call at once: the look-up runs under a lock
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
     if (g_decode_static_ptr[device] == nullptr) {
         float* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress((void**)&p, g_decode_static_scratch);

@@ -152,6 +152,10 @@ class _DecodeGraph:
         if runner._graph_pool is None:
             runner._graph_pool = self.graph.pool()
 
+    def forget_rows(self) -> None:
+        """Every row's block table is written afresh at its next use."""
+        self.row_owner = [-1] * self.bucket
+
     def fill(self, runner: "ModelRunner", entries: Sequence[StepEntry], host_tokens: bool) -> None:
         """Write this step's indices into the pinned buffer and send it.  A row keeps the
         block table of the request it held last step; only pages added since are written."""
@@ -445,22 +449,29 @@ class ModelRunner:
         before they are fed back.  With `borrow_logits` the result may be a view of a buffer
         that the next step overwrites (for callers that consume it at once)."""
         self._validate(entries)
-        self.cache.reserve([(e.request_id, len(e.tokens)) for e in entries])
-        self._zero_new_state()
-        bucket = self._bucket_for(entries)
-        if bucket:
-            logits = self._graph_step(entries, bucket, device_tokens)
-            if logits is not None and not borrow_logits:
-                logits = logits.clone()
-        else:
-            step, rows = self._build(entries)
-            if device_tokens is not None:
-                if not step.decode_only:
-                    raise StepError("device_tokens only stands for steps of single tokens")
-                step.token_ids[: step.num_tokens].copy_(device_tokens[: step.num_tokens])
-            logits = self.model.forward(step, self.entry_caches, rows)
-        for e in entries:
-            self.cache.commit(e.request_id, len(e.tokens))
+        lease = self.cache.lease([(e.request_id, len(e.tokens)) for e in entries])
+        try:
+            self._zero_new_state()
+            bucket = self._bucket_for(entries)
+            if bucket:
+                logits = self._graph_step(entries, bucket, device_tokens)
+                if logits is not None and not borrow_logits:
+                    logits = logits.clone()
+            else:
+                step, rows = self._build(entries)
+                if device_tokens is not None:
+                    if not step.decode_only:
+                        raise StepError("device_tokens only stands for steps of single tokens")
+                    step.token_ids[: step.num_tokens].copy_(device_tokens[: step.num_tokens])
+                logits = self.model.forward(step, self.entry_caches, rows)
+        except BaseException:
+            # the step did not happen: its pages go back, and no captured step may trust a
+            # block table it wrote earlier (tables have shrunk under it)
+            lease.release()
+            for g in self._graphs.values():
+                g.forget_rows()
+            raise
+        lease.commit()
         self.steps_run += 1
         return logits
 

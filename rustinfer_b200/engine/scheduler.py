@@ -160,8 +160,11 @@ class Scheduler:
         self.waiting.appendleft(victim)
         plan.preempted.append(victim.request_id)
 
-    def schedule(self) -> StepPlan:
-        plan = StepPlan([])
+    def schedule(self, _gave_way: Sequence[Any] = ()) -> StepPlan:
+        """The next step's batch.  `_gave_way`: requests a first pass of this very call
+        preempted (the call starts over once when nothing could move); they count as
+        preempted by the plan that is returned and are not admitted again by it."""
+        plan = StepPlan([], list(_gave_way))
         taken: Dict[int, int] = {}
         budget = self.max_batch_tokens
 
@@ -206,6 +209,10 @@ class Scheduler:
             req = self.waiting[0]
             if req.request_id in plan.preempted:          # it just gave way; not back in the same step
                 break
+            if req.undelivered:
+                # it gave way while a token of its own was still on the way to the host: its
+                # sequence is not complete yet, so it cannot be recomputed before that arrives
+                break
             total = len(req.prompt) + len(req.output)
             if any(k > self.cache.pools[g].num_pages
                    for g, k in self.cache.pages_needed_fresh(total + 1).items()):
@@ -238,7 +245,7 @@ class Scheduler:
                 self._fail(self.running[0], "kv_pool_exhausted")
             else:
                 self._preempt(max(self.running, key=lambda r: r.admitted_at), plan)
-            return self.schedule() if self.has_work() else plan
+            return self.schedule(plan.preempted) if self.has_work() else plan
         return plan
 
     # ------------------------------------------------------------------ after the step

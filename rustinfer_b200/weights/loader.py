@@ -33,8 +33,14 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+# Buffers that some exporters of Llama checkpoints write beside the weights; they are derived
+# from the configuration, no model declares them, and a file that has them is not at fault.
+# Anything else the model does not know stays an error.
+IGNORED_SUFFIXES = ("rotary_emb.inv_freq",)
+
+
 def check_against(reader: SafetensorsReader, decls: Mapping[str, ParamDecl], folder: str) -> None:
-    have = set(reader.names())
+    have = set(n for n in reader.names() if not n.endswith(IGNORED_SUFFIXES))
     missing = sorted(n for n, d in decls.items() if n not in have and not d.optional)
     unexpected = sorted(have - set(decls))
     wrong = [f"{n}: expected {list(decls[n].shape)}, got {list(reader.shape(n))}"

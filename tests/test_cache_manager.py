@@ -139,3 +139,45 @@ def test_slots_run_out_before_pages():
     with pytest.raises(KeyError):
         m.open(1)
     assert m.newly_opened_slots == [0, 1]
+
+
+def test_a_lease_gives_its_pages_back_when_the_step_fails():
+    """Pages reserved for a step that then raises are neither kept nor lost: tables, lengths and
+    the pool are as before; a step that succeeds owns them; a lease is settled once."""
+    import pytest
+    from rustinfer_b200.cache.manager import CacheLayout, CacheManager
+    from rustinfer_b200.parts.base import PagedKV
+    lay = CacheLayout.from_needs([(0, PagedKV(1, 16, None), None), (1, PagedKV(1, 16, 6), None)])
+    cache = CacheManager(lay, [8, 8], 4, 3)
+    cache.open("a"), cache.open("b")
+    with cache.lease([("a", 6), ("b", 3)]):
+        pass                                                # the step ran
+    assert cache.length("a") == 6 and cache.length("b") == 3
+    before = ({g: list(cache.block_table(r, g)) for r in "ab" for g in (0, 1)}, cache.free_pages())
+    with pytest.raises(RuntimeError, match="kernel"):
+        with cache.lease([("a", 7), ("b", 1)]) as lease:
+            assert cache.free_pages()[0] < before[1][0]     # checked out
+            raise RuntimeError("a kernel gave up")          # the failure is made on the host
+    assert lease.settled
+    assert ({g: list(cache.block_table(r, g)) for r in "ab" for g in (0, 1)}, cache.free_pages()) == before
+    assert cache.length("a") == 6 and cache.length("b") == 3
+    cache.check_invariants()
+    # the same step again, now clean: same pages as the failed try had (smallest first)
+    with cache.lease([("a", 7), ("b", 1)]):
+        pass
+    assert cache.length("a") == 13 and cache.pages_held("a")[0] == 4
+    cache.check_invariants()
+    # a request closed while its lease is open (an abort): nothing is freed twice
+    lease = cache.lease([("b", 9)])
+    cache.close("b")
+    lease.release()
+    cache.check_invariants()
+    with pytest.raises(RuntimeError, match="already"):
+        lease.commit()
+    # all or nothing still holds
+    from rustinfer_b200.cache.pages import OutOfPages
+    with pytest.raises(OutOfPages):
+        cache.lease([("a", 100)])
+    cache.check_invariants()
+    cache.close("a")
+    assert cache.free_pages() == {0: 8, 1: 8}

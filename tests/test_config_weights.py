@@ -131,6 +131,8 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del w["lm_head.weight"]                                  # untied model: the head is required
     w["model.layers.0.self_attn.q_norm.weight"] = torch.ones(32)
     w["model.layers.2.self_attn.k_proj.weight"] = torch.zeros(16, 96)
+    # a buffer some exporters write beside the weights: derived from the configuration, not a fault
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(16)
     write_model(str(tmp_path), TINY_B, w)
     with pytest.raises(WeightError) as ei:
         check_against(SafetensorsReader(str(tmp_path)), _decls(TINY_B), str(tmp_path))
@@ -204,3 +206,9 @@ def test_run_file(tmp_path):
     p.write_text('max_batch_seqs = 4\n')
     with pytest.raises(RunConfigError, match="model"):
         RunConfig.load(str(p))
+    # paths inside the run file are relative to the run file, wherever the program is started
+    p.write_text('[random_weights]\nconfig = "cfgs/tiny.json"\nseed = 1\n')
+    cfg = RunConfig.load(str(p))
+    assert cfg.random_weights["config"] == str(tmp_path / "cfgs" / "tiny.json") and cfg.model == ""
+    p.write_text('[random_weights]\nconfig = "/abs/tiny.json"\n')
+    assert RunConfig.load(str(p)).random_weights["config"] == "/abs/tiny.json"

@@ -588,6 +588,64 @@ def test_attention_tc_finds_one_far_key():
         assert float((out.double().cpu()[0] - want).abs().max()) < 0.05, far
 
 
+def _poison_before_window(case, window):
+    """Keys no row of an entry may see (before the window of its first row) become NaN, keys and
+    values alike, whole pages where the window has passed them: what a request finds where its
+    given-back pages used to be."""
+    cache = case.cache.cpu()
+    table = case.table.cpu()
+    for b, (n_kv, n_q) in enumerate(zip(case.kv_lens, case.q_lens)):
+        lo = max(0, (n_kv - n_q) - window + 1)
+        for key in range(lo):
+            cache[int(table[b, key // case.page]), :, :, key % case.page] = float("nan")
+    case.cache = cache.to(dev())
+
+
+@pytest.mark.parametrize("window", [5, 40, 100, 130])
+@pytest.mark.parametrize("Hq,Hkv,hd,page", [(8, 2, 64, 16), (4, 1, 128, 16), (6, 2, 128, 8), (8, 8, 64, 64)])
+@pytest.mark.parametrize("path", ["decode_tma", "decode_cp_async", "prefill_tc", "prefill_mma"])
+def test_attention_window_never_reads_what_lies_before_it(path, Hq, Hkv, hd, page, window):
+    """Head sizes 64 and 128 (the kernels that fetch by TMA), a window, and NaN in every key
+    and value before it: a probability of zero must not meet them."""
+    k = K()
+    kv_lens = [70, 9, 40, 200, 300, 515, 131]
+    q_lens = [30, 9, 1, 1, 150, 1, 1]
+    case = PagedCase(BF, Hq, Hkv, hd, page, kv_lens, q_lens, seed=window + hd, poison=True)
+    _poison_before_window(case, window)
+    out = torch.full_like(case.q_all, float("nan"))
+    ref = case.reference(0.2, window)
+    rows = []
+    at = 0
+    for n in q_lens:
+        rows.append((at, n)); at += n
+    if path.startswith("decode"):
+        dec = [b for b, n in enumerate(q_lens) if n == 1]
+        splits = 3
+        no, nl = k.decode_scratch_floats(len(dec), Hq, hd, splits)
+        k.attention_decode_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len,
+                                torch.tensor(dec, dtype=torch.int32, device=dev()), len(dec), Hq, Hkv, hd, 0.2,
+                                window, splits, torch.full((no,), float("nan"), device=dev()),
+                                torch.full((nl,), float("nan"), device=dev()), by_tma=path == "decode_tma")
+        keep = [rows[b][0] for b in dec]
+    else:
+        if path == "prefill_tc":
+            if not k.tc_attention_supports(Hq, Hkv, hd, page):
+                pytest.skip("geometry not taken by the tcgen05 kernel")
+            te, tq = _mma_tiles(case, k.tc_tokens_per_tile(Hq, Hkv), skip_decode=False)
+            k.attention_prefill_tc(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                                   Hq, Hkv, hd, 0.2, window)
+        else:
+            te, tq = _mma_tiles(case, k.mma_tokens_per_tile(Hq, Hkv), skip_decode=False)
+            k.attention_prefill_bf16(case.q_all, out, case.cache, case.table, case.cu_q, case.kv_len, te, tq,
+                                     Hq, Hkv, hd, 0.2, window)
+        keep = list(range(out.shape[0]))
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+    idx = torch.tensor(keep)
+    assert not torch.isnan(out[idx.to(dev())]).any()
+    close_attention(out[idx.to(dev())], case, ref[idx])
+
+
 @pytest.mark.parametrize("V", [130, 391, 128256])
 def test_argmax_lowest_index_wins(V):
     torch.manual_seed(5)

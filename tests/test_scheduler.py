@@ -188,3 +188,170 @@ def test_decisions_are_deterministic():
         return [[(e.request.request_id, e.start, e.count) for e in p.entries] + p.preempted
                 for p in run(cache, s)]
     assert trace() == trace()
+
+
+# ------------------------------------------------ one step late: advance at launch, deliver later
+# The engine launches step N+1 before it has read the tokens step N chose (they are fed back
+# on the device), so the scheduler plans with tokens that are chosen but not yet delivered.
+# This stand-in drives `schedule / advance / deliver` exactly in the engine's order, with the
+# "device" knowing the undelivered tokens and the scheduler not.
+
+def run_one_step_late(cache, sched, max_steps=10_000, on_plan=None):
+    from rustinfer_b200.engine.scheduler import FINISHED
+    inflight = None                       # (plan, tokens the device chose, the requests that sampled)
+    on_device = {}                        # request id -> tokens chosen but not delivered
+    steps = 0
+
+    def resolve():
+        nonlocal inflight
+        plan, toks, _ = inflight
+        inflight = None
+        sched.deliver(plan, toks)
+        for e in plan.entries:
+            if e.samples:
+                on_device[e.request.request_id].pop(0)
+
+    while sched.has_work() or inflight is not None:
+        plan = sched.schedule()
+        if on_plan:
+            on_plan(plan)
+        chain = (inflight is not None and plan.entries and len(plan.entries) == len(inflight[2])
+                 and all(e.count == 1 and e.samples and e.request is q for e, q in zip(plan.entries, inflight[2])))
+        if inflight is not None and not chain:
+            resolve()
+            plan.entries = [e for e in plan.entries if e.request.state != FINISHED]
+        if not plan.entries:
+            steps += 1
+            assert steps < max_steps
+            continue
+        cache.reserve([(e.request.request_id, e.count) for e in plan.entries])
+        chosen, samplers = [], []
+        for e in plan.entries:
+            rid = e.request.request_id
+            assert e.start == cache.length(rid), (rid, e.start, cache.length(rid))
+            cache.commit(rid, e.count)
+            if e.samples:
+                seq = e.request.sequence + on_device.get(rid, [])
+                assert e.start + e.count == len(seq), (rid, e.start, e.count, len(seq))
+                tok = next_token(seq)
+                on_device.setdefault(rid, []).append(tok)
+                chosen.append(tok), samplers.append(e.request)
+        sched.advance(plan)
+        if chain:
+            resolve()
+        inflight = (plan, chosen, samplers) if samplers else None
+        cache.check_invariants()
+        steps += 1
+        assert steps < max_steps
+    return steps
+
+
+def _pressure(n_req=4, pages=9, page=4, seqs=3, max_tokens=9, eos=()):
+    cache, s = make(pages=pages, page=page, seqs=seqs, tokens=32, chunk=6, eos=eos)
+    reqs = [Request(i, [i + 1, 2, 3, 4, 5, 6, 7][: 4 + i % 3], SamplingParams(max_tokens=max_tokens))
+            for i in range(n_req)]
+    for r in reqs:
+        s.add(r)
+    return cache, s, reqs
+
+
+def test_one_step_late_gives_the_tokens_of_the_unpipelined_run_under_page_pressure():
+    for pages in (5, 6, 7, 9, 12, 40):
+        cache, s, reqs = _pressure(pages=pages)
+        run_one_step_late(cache, s)
+        cache2, s2, reqs2 = _pressure(pages=pages)
+        run(cache2, s2)
+        for a, b in zip(reqs, reqs2):
+            assert a.finish_reason == b.finish_reason == "length", pages
+            assert a.output == b.output == expected(a.prompt, 9), (pages, a.request_id)
+            assert a.undelivered <= 1
+        assert cache.free_pages() == {0: pages} and cache.slots.free_count == 3
+        if pages <= 7:
+            assert s.num_preemptions > 0
+
+
+def test_one_step_late_stop_token_and_max_tokens_in_flight():
+    # every request's 4th token is made a stop id: it is chosen while a later step is planned
+    probe = [expected([i + 1, 2, 3, 4, 5, 6, 7][: 4 + i % 3], 9) for i in range(4)]
+    eos = sorted({p[3] for p in probe})
+    cache, s, reqs = _pressure(pages=40, eos=eos)
+    run_one_step_late(cache, s)
+    for r, p in zip(reqs, probe):
+        cut = next(i for i, t in enumerate(p) if t in eos)
+        assert r.output == p[: cut + 1] and r.finish_reason == "stop"
+    assert cache.free_pages() == {0: 40}
+    # max_tokens 1 and 2: the last token is in flight when the next plan is made
+    for mt in (1, 2):
+        cache, s, reqs = _pressure(pages=40, max_tokens=mt)
+        run_one_step_late(cache, s)
+        assert all(r.output == expected(r.prompt, mt) and r.finish_reason == "length" for r in reqs)
+
+
+def test_a_victim_with_a_token_in_flight_is_not_readmitted_before_it_arrives():
+    """Preempted with undelivered == 1 (also while DRAINING): the plan that preempts it, and a
+    plan made by starting over in the same call, leave it waiting; its tokens match."""
+    from rustinfer_b200.engine.scheduler import DRAINING, WAITING
+    seen = {"victim_in_flight": 0, "draining_victim": 0}
+    was_draining = set()
+
+    def watch(plan):
+        for r in list(s.waiting):
+            if r.request_id in plan.preempted and r.undelivered:
+                seen["victim_in_flight"] += 1
+                if r.request_id in was_draining:
+                    seen["draining_victim"] += 1
+                assert all(e.request is not r for e in plan.entries)
+        was_draining.clear()
+        was_draining.update(r.request_id for r in s.running if r.state == DRAINING)
+
+    for pages in (5, 6, 7):
+        for mt in (3, 5, 9):
+            cache, s, reqs = _pressure(n_req=5, pages=pages, max_tokens=mt)
+            run_one_step_late(cache, s, on_plan=watch)
+            for r in reqs:
+                assert r.output == expected(r.prompt, mt), (pages, mt, r.request_id)
+            assert cache.free_pages() == {0: pages}
+    assert seen["victim_in_flight"] > 0
+
+
+def test_starting_over_keeps_the_list_of_preempted_requests():
+    # two requests fill the pool so that neither can grow: the younger gives way in a first
+    # pass, the call starts over, and the plan it returns still names it and does not readmit it
+    cache, s = make(pages=4, page=4, seqs=2, tokens=64)
+    a = Request("a", [1] * 8, SamplingParams(max_tokens=8))
+    b = Request("b", [2] * 8, SamplingParams(max_tokens=8))
+    s.add(a), s.add(b)
+    p = s.schedule()
+    cache.reserve([(e.request.request_id, e.count) for e in p.entries])
+    for e in p.entries:
+        cache.commit(e.request.request_id, e.count)
+    s.complete_step(p, [1, 1])
+    p = s.schedule()                                       # both need a fifth page... there is none
+    assert "b" in p.preempted and [e.request.request_id for e in p.entries] == ["a"]
+    assert s.waiting[0] is b
+
+
+def test_a_draining_victim_of_a_start_over_finishes_from_the_waiting_queue():
+    # b's prompt is stuck one token short of a page it cannot get; c, younger, has chosen its
+    # only token but the host has not read it.  Nothing can move, so c gives way, the call
+    # starts over, and the plan it returns must not readmit c (its token is still on the way).
+    from rustinfer_b200.engine.scheduler import DRAINING, FINISHED
+    cache, s = make(pages=4, page=4, seqs=2, tokens=64, chunk=8)
+    b = Request("b", [2] * 9, SamplingParams(max_tokens=2))
+    c = Request("c", [3] * 5, SamplingParams(max_tokens=1))
+    s.add(b), s.add(c)
+    p0 = s.schedule()
+    assert [(e.request.request_id, e.count, e.samples) for e in p0.entries] == [("b", 8, False), ("c", 5, True)]
+    cache.reserve([("b", 8), ("c", 5)]), cache.commit("b", 8), cache.commit("c", 5)
+    s.advance(p0)                                           # launched; c's token is not delivered yet
+    assert c.state == DRAINING and c.undelivered == 1 and cache.free_pages() == {0: 0}
+    p1 = s.schedule()
+    assert p1.preempted == ["c"] and [e.request.request_id for e in p1.entries] == ["b"]
+    assert s.waiting[0] is c and not cache.is_open("c")
+    s.deliver(p0, [next_token(c.prompt)])
+    assert c.state == FINISHED and c.output == expected(c.prompt, 1) and not s.waiting
+    cache.reserve([("b", 1)]), cache.commit("b", 1)
+    s.complete_step(p1, [next_token(b.prompt)])
+    run(cache, s)
+    assert b.output == expected(b.prompt, 2) and cache.free_pages() == {0: 4}
+    cache.check_invariants()

@@ -7,8 +7,9 @@ the library through its C symbols and have no allocator to lend.  For them
 `ri_attention_decode_bf16_static` keeps the split-KV scratch in a 4 MiB array inside the
 library.  This test calls it through its exported C symbol, twice in a row on different
 data (the second call finds the first call's leftovers in the shared array), and holds its
-output to the existing entry point's within the tolerance of the kernel tests; it also
-checks that a request beyond the array's size is refused with a message.
+output to the existing entry point's, and to a float64 statement of the same attention
+from the plain implementation, within the tolerance of the kernel tests; it also checks
+that a request beyond the array's size is refused with a message.
 
 It is collected last, so that a run that stops at the first failure has run every other
 test before it.
@@ -35,9 +36,11 @@ def _case(seed, entries, Hq, Hkv, hd, page, kv_lens):
     cache = torch.full((n_pages, 2, Hkv, page, hd), float("nan"), dtype=torch.bfloat16)
     table = torch.zeros(entries, max(blocks), dtype=torch.int32)
     at = 0
+    keys, values = [], []
     for b, n in enumerate(kv_lens):
         k = torch.randn(n, Hkv, hd, generator=g).bfloat16()
         v = torch.randn(n, Hkv, hd, generator=g).bfloat16()
+        keys.append(k); values.append(v)
         for j in range(blocks[b]):
             pg = perm[at]; at += 1
             table[b, j] = pg
@@ -47,7 +50,18 @@ def _case(seed, entries, Hq, Hkv, hd, page, kv_lens):
     q = torch.randn(entries, Hq * hd, generator=g).bfloat16()
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
     return dict(q=q.to(dev), cache=cache.to(dev), table=table.to(dev), cu_q=i32(list(range(entries + 1))),
-                kv_len=i32(kv_lens))
+                kv_len=i32(kv_lens), q_host=q, keys=keys, values=values)
+
+
+def _float64_statement(c, Hq, hd, scale):
+    """The entry's one query sees all of its keys: the last row of whole-sequence attention."""
+    import plain_llama
+    rows = []
+    for b, (k, v) in enumerate(zip(c["keys"], c["values"])):
+        qfull = torch.zeros(k.shape[0], Hq, hd, dtype=torch.float64)
+        qfull[-1] = c["q_host"][b].double().view(Hq, hd)
+        rows.append(plain_llama.causal_gqa_attention(qfull, k.double(), v.double(), scale)[-1].reshape(-1))
+    return torch.stack(rows)
 
 
 def test_static_scratch_entry_point_matches_the_allocating_one():
@@ -80,6 +94,12 @@ def test_static_scratch_entry_point_matches_the_allocating_one():
         assert not torch.isnan(got).any()
         scale_ref = float(want.float().abs().max())
         assert float((got.float() - want.float()).abs().max()) <= 2 ** -8 * scale_ref, f"call {call}"
+        # and against the plain statement, by the bound the attention kernels' own tests use:
+        # one rounding of the output and one of each probability, 2^-9 (max|out| + max|v|)
+        ref = _float64_statement(c, Hq, hd, scale)
+        vmax = max(float(v.double().abs().max()) for v in c["values"])
+        bound = 2 ** -9 * (float(ref.abs().max()) + vmax)
+        assert float((got.double().cpu() - ref).abs().max()) <= bound, f"call {call}"
     # beyond the array: refused, nothing launched, the reason is told
     too_many = SCRATCH_FLOATS // (Hq * 16 * (hd + 1)) + 1
     rc = fn(None, 0, None, 0, None, None, 0, None, None, None, too_many, Hq, Hkv, page, scale, 0, 16, stream)
