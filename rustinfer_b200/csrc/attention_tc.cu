@@ -25,6 +25,7 @@
 // Every wait on an mbarrier is bounded; a time-out leaves a code in *error and the kernel
 // winds down (tensor memory freed, copies in flight drained).
 #include "common.cuh"
+#include "tc_primitives.cuh"
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -34,6 +35,7 @@
 #endif
 
 namespace {
+using namespace ri_tc;                    // mbarriers with bounded waits, TMA loads, tcgen05 fences, commit, MMA
 constexpr int HD = RI_HEAD_DIM;
 static_assert(HD == 64 || HD == 128, "tcgen05 attention: head size 64 or 128");
 constexpr int BM = 128;                   // rows per CTA (MMA M)
@@ -41,7 +43,6 @@ constexpr int BN = 64;                    // keys per tile
 constexpr int KB = HD / 64;               // 64-wide column blocks of a head (one 128-byte swizzle row each)
 constexpr int NS = 2;                     // stages of K and of V
 constexpr int THREADS = 192;
-constexpr unsigned SPIN_LIMIT = 1u << 20;
 constexpr int TMEM_COLS = HD == 64 ? 128 : 256;   // S: 64 columns, O: HD columns
 constexpr int COL_S = 0, COL_O = BN;
 constexpr float RESCALE_STEP = 8.0f;              // log2 of the growth of a row's maximum that forces a rescale
@@ -55,43 +56,6 @@ constexpr size_t SMEM = (size_t)OFF_BAR + 512 + 1024 /*alignment*/;
 
 enum { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13 };
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                 "selp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* error, int code) {
-#pragma unroll 1
-    for (unsigned i = 0; i < SPIN_LIMIT; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 1024) __nanosleep(64);
-    }
-    atomicExch(error, code);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Shared-memory descriptors, 128-byte swizzle, 8-row groups 1024 bytes apart.
@@ -107,10 +71,7 @@ __device__ __forceinline__ uint64_t desc_mnmajor(unsigned addr) {
            ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 __device__ __forceinline__ void mma_ss(unsigned tmem_d, uint64_t a, uint64_t b, unsigned idesc, unsigned accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\t"
-                 "setp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+    mma_bf16_ss(tmem_d, a, b, idesc, accumulate);
 }
 // 16 consecutive fp32 columns of this thread's lane into r[0..15] (complete after tmem_ld_wait)
 __device__ __forceinline__ void tmem_ld16_issue(unsigned addr, float* r) {

@@ -53,6 +53,21 @@ __device__ __forceinline__ float block_sum(float v, float* red /* >= 33 floats *
 
 static inline int ri_launch_status() { return (int)cudaGetLastError(); }
 
+// Streaming multiprocessors of the current device (asked once per library and device change is
+// not expected within a process: one process drives one GPU).
+static inline int ri_device_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+            sms = n;
+        else
+            return 1;                                     // no device yet: ask again next time
+    }
+    return sms;
+}
+
 // ---- programmatic dependent launch -------------------------------------------------
 // Kernels of one step run back to back on one stream.  Launched with the programmatic-
 // serialization attribute, a kernel may begin (set up barriers, fetch weights that no

@@ -190,7 +190,7 @@ RI_API int ri_residual_add(float* h, const void* delta, int act_dtype, long long
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     int blocks = (int)((n + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > ri_device_sms() * 8) blocks = ri_device_sms() * 8;
     if (act_dtype == RI_BF16) RI_CHECKED(ri_launch(residual_add_kernel<bf16>, dim3(blocks), dim3(256), 0, s, h, (const bf16*)delta, (size_t)n));
     else RI_CHECKED(ri_launch(residual_add_kernel<float>, dim3(blocks), dim3(256), 0, s, h, (const float*)delta, (size_t)n));
     return ri_launch_status();
@@ -387,7 +387,7 @@ RI_API int ri_silu_mul(const void* gu, void* out, int act_dtype, int tokens, int
     if (act_dtype == RI_BF16 && inter % 8 == 0 && aligned16(gu) && aligned16(out)) {
         const size_t n_vec = (size_t)tokens * (inter / 8);
         size_t blocks = (n_vec + 255) / 256;
-        if (blocks > 148 * 16) blocks = 148 * 16;
+        if (blocks > (size_t)ri_device_sms() * 16) blocks = (size_t)ri_device_sms() * 16;
         RI_CHECKED(ri_launch(silu_mul_bf16x8_kernel, dim3((int)blocks), dim3(256), 0, s, (const bf16*)gu, (bf16*)out, inter, n_vec));
         return ri_launch_status();
     }

@@ -640,15 +640,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-int device_sms() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
+int device_sms() { return ri_device_sms(); }
 
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, cudaStream_t s) {
     static bool configured = false;
@@ -738,7 +730,7 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     // the half-SM one that lets the next product move in early: 525 MB at batch 8 took 98 us with
     // 96 KB and 85.7 us (6.1 TB/s) with 160 KB
     if (swap && bn <= 64 && g_stream_budget < SMEM_BUDGET_LONG &&
-        (double)p.a_rows * K * 2 / 148.0 > 1048576.0) p.budget = SMEM_BUDGET_LONG;
+        (double)p.a_rows * K * 2 / (double)device_sms() > 1048576.0) p.budget = SMEM_BUDGET_LONG;
     p.stages = p.budget / p.stage_bytes;
     if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
     p.stages &= ~1;                                       // stages are released in pairs

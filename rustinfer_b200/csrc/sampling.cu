@@ -243,7 +243,7 @@ RI_API int ri_argmax(const float* logits, int ld, int rows, int vocab, int* out,
                      unsigned long long* state, unsigned int* count, void* stream) {
     if (rows <= 0) return 0;
     int per_row = (vocab + 2047) / 2048;                 // 8 elements per thread
-    const int cap = (4 * 148 + rows - 1) / rows;         // about four CTAs per SM in all
+    const int cap = (4 * ri_device_sms() + rows - 1) / rows;         // about four CTAs per SM in all
     if (per_row > cap) per_row = cap;
     if (per_row < 1) per_row = 1;
     RI_CHECKED(ri_launch(argmax_kernel, dim3(dim3(per_row, rows)), dim3(256), 0, (cudaStream_t)stream, logits, ld, vocab, out, state, count));

@@ -48,13 +48,14 @@ class _InFlight:
     samplers: List[Request]
     turn: int                           # which result buffer its tokens land in
     event: Any
-    lazy: bool                          # all rows greedy: its tokens may be read after the next launch
+    lazy: bool                          # its tokens may be read after the next launch
 
 
 @dataclass
 class EngineStats:
     stop_flag_mismatches: int = 0
     steps: int = 0
+    chained_steps: int = 0              # steps launched with the step before still unread by the host
     prompt_tokens: int = 0
     generated_tokens: int = 0
     preemptions: int = 0
@@ -123,10 +124,11 @@ class Engine:
     def step(self) -> List[StepOutput]:
         """One iteration: schedule a batch, launch it, choose tokens on the device.
 
-        A step whose rows are all greedy leaves its tokens on the device (`_inflight`): the
-        stop check runs there, the tokens are fed to the next step there, and the host reads
-        them only after it has launched that next step, so planning and launching overlap
-        the GPU's work.  The tokens a call returns are therefore those of the step before
+        A step leaves its tokens on the device (`_inflight`), greedy or drawn (a row's uniform
+        draw is a function of the request's seed and the token's position, both known to the
+        host before the token is): the stop check runs there, the tokens are fed to the next
+        step there, and the host reads them only after it has launched that next step, so
+        planning and launching overlap the GPU's work.  The tokens a call returns are therefore those of the step before
         the one it launched; `has_unfinished()` stays true until the last ones are read.
         This is the engine's counterpart of RustInfer's one-deep device-resident decode
         pipeline (crates/infer-worker/src/application/runtime/abc_decode.rs:77-89,109-)."""
@@ -167,9 +169,10 @@ class Engine:
             self._result_host[k][: 2 * n].copy_(self._result_dev[k][: 2 * n], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record()
-            launched = _InFlight(plan, samplers, k, ev, all(q.params.is_greedy() for q in samplers))
+            launched = _InFlight(plan, samplers, k, ev, True)
         sched.advance(plan)
         self.stats.steps += 1
+        self.stats.chained_steps += 1 if chain else 0
         self.stats.prompt_tokens += sum(e.count for e in plan.entries) - sum(
             1 for e in plan.entries if e.count == 1 and (e.request.output or e.request.undelivered > 1))
         if chain:
@@ -186,7 +189,7 @@ class Engine:
         prev = self._inflight
         if not prev.lazy or len(plan.entries) != len(prev.samplers) or not plan.entries:
             return False
-        return all(e.count == 1 and e.samples and e.request is q and q.params.is_greedy()
+        return all(e.count == 1 and e.samples and e.request is q
                    for e, q in zip(plan.entries, prev.samplers))
 
     def _resolve(self) -> List[StepOutput]:

@@ -26,7 +26,7 @@ from ..cache.pages import OutOfPages
 from ..config.registry import load_model_description
 from ..models.decoder import Decoder
 from ..parts.base import (BuildContext, FixedState, GroupStep, HostEntry, PagedKV, PagedLayerCache,
-                          StateLayerCache, StepContext)
+                          StateLayerCache, StepContext, StepShape)
 from ..weights.loader import load_weights
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -88,13 +88,16 @@ class _DecodeGraph:
         self.bucket = bucket
         P = runner.max_pages_per_request
         groups = runner.layout.paged_groups()
-        # fixed layout: token_ids, positions, cu_q, kv_len, slots, rows, [table, slot_of_token]*, decode list, tiles
+        self.spare_slot = runner.max_batch_seqs               # the state row padding rows point at
+        # what the parts' index arrays look like for `bucket` rows of one token each
+        shape = self._shape(np.zeros(bucket, dtype=np.int64), np.full(bucket, self.spare_slot, dtype=np.int64))
+        built = [(need, need.build(shape)) for need in runner.index_needs]
+        # fixed layout: token_ids, positions, cu_q, kv_len, slots, rows, [table, slot_of_token]*, index arrays
         sizes = [bucket, bucket, bucket + 1, bucket, bucket, bucket]
         for _ in groups:
             sizes += [bucket * P, bucket]
-        sizes.append(bucket)
-        for _ in runner.tile_rows:
-            sizes += [bucket, bucket]
+        for _need, arrays in built:
+            sizes += [int(a.size) for a in arrays]
         self.offsets = []
         at = 0
         for n in sizes:
@@ -113,6 +116,7 @@ class _DecodeGraph:
         h_rows[:] = np.arange(bucket)
         self.h_pos[:] = 0
         self.h_kv[:] = 1
+        self.h_slots[:] = self.spare_slot
         it, hit = iter(v[6:]), iter(hv[6:])
         gsteps, self.h_tables, self.h_slot_of_token = [], [], []
         for _ in groups:
@@ -121,19 +125,23 @@ class _DecodeGraph:
             h = next(hit)
             h[:] = -1
             self.h_slot_of_token.append(h)
-        decode_entries = next(it)
-        next(hit)[:] = np.arange(bucket)
-        tiles = {}
-        for r in runner.tile_rows:
-            tiles[r] = (next(it), next(it))
-            next(hit)[:] = np.arange(bucket)
-            next(hit)[:] = 0
+        indices = {}
+        self.moving_indices = []                             # (need, host views): made anew at every replay
+        for need, arrays in built:
+            devs, hosts = [], []
+            for a in arrays:
+                devs.append(next(it))
+                h = next(hit)
+                h[:] = a
+                hosts.append(h)
+            indices[need.key] = tuple(devs)
+            if need.depends_on_positions:
+                self.moving_indices.append((need, hosts))
         self.dev.copy_(self.host)
         self.step = StepContext(
             num_tokens=bucket, num_entries=bucket, token_ids=v[0], positions=v[1], cu_q=v[2], kv_len=v[3],
-            state_slots=v[4], groups=gsteps, tiles=tiles, entries=[], max_q_len=1,
-            max_kv_len=runner.max_model_len, decode_only=True, decode_entries=decode_entries,
-            num_decode=bucket, prefill_tiles={r: (v[0][:0], v[0][:0]) for r in runner.prefill_tile_rows})
+            state_slots=v[4], groups=gsteps, entries=[], max_q_len=1,
+            max_kv_len=runner.max_model_len, decode_only=True, indices=indices)
         self.rows = v[5]
         # one eager run (libraries pick their algorithms, lazy kernels get built), then capture
         torch.cuda.synchronize()
@@ -151,6 +159,10 @@ class _DecodeGraph:
         self.kernels_per_replay = _lib.launch_count - before
         if runner._graph_pool is None:
             runner._graph_pool = self.graph.pool()
+
+    def _shape(self, pos0: np.ndarray, slots: np.ndarray) -> StepShape:
+        ones = np.ones(self.bucket, dtype=np.int64)
+        return StepShape(ones, pos0, np.arange(self.bucket + 1, dtype=np.int64), pos0 + 1, slots)
 
     def forget_rows(self) -> None:
         """Every row's block table is written afresh at its next use."""
@@ -194,8 +206,18 @@ class _DecodeGraph:
                 self.h_pos[i] = 0
                 self.h_kv[i] = 1
                 self.h_tokens[i] = 0
+                self.h_slots[i] = self.spare_slot            # no live request's state is touched
                 for h in self.h_slot_of_token:
                     h[i] = -1
+        if self.moving_indices:
+            shape = self._shape(self.h_pos.astype(np.int64), self.h_slots.astype(np.int64))
+            for need, hosts in self.moving_indices:
+                arrays = need.build(shape)
+                if [int(a.size) for a in arrays] != [h.size for h in hosts]:
+                    raise StepError(f"index arrays {need.key!r} change their lengths between steps of "
+                                    f"{self.bucket} single tokens; such a part cannot run from a captured step")
+                for h, a in zip(hosts, arrays):
+                    h[:] = a
         self.dev.copy_(self.host, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
@@ -244,13 +266,12 @@ class ModelRunner:
         self.cache = CacheManager(self.layout, [self.num_pages] * len(paged), self.page_size,
                                   self.max_batch_seqs)
         self._alloc_storage()
-        self.tile_rows = self.model.attention_tile_rows()
-        self.prefill_tile_rows = self.model.prefill_tile_rows()
+        self.index_needs = self.model.step_indices()          # arrays the parts want made for every step
         cap_t, cap_b = self.max_batch_tokens, self.max_batch_seqs
         n_ints = 5 * cap_t + 5 * cap_b + 64
         n_ints += len(paged) * (cap_b * self.max_pages_per_request + cap_t + 16)
-        for r in self.tile_rows + self.prefill_tile_rows:
-            n_ints += 2 * (cap_t // r + cap_b + 8)
+        for need in self.index_needs:
+            n_ints += int(need.capacity(cap_t, cap_b)) + 32
         self._staging = _Staging(n_ints, self.device)
         # per-request counters the device keeps by state slot: {generated, max_tokens, ignore_eos, last_token}
         self.slot_state = torch.zeros((self.max_batch_seqs, 4), dtype=torch.int32, device=self.device)
@@ -295,7 +316,8 @@ class ModelRunner:
                 t = torch.zeros((n, self.num_pages, 2, g.need.num_kv_heads, self.page_size, g.need.head_dim),
                                 dtype=self.dtype, device=self.device)
             elif isinstance(g.need, FixedState):
-                t = torch.zeros((n, self.max_batch_seqs) + tuple(g.need.shape),
+                # one row more than there are slots: padding rows of a captured step point there
+                t = torch.zeros((n, self.max_batch_seqs + 1) + tuple(g.need.shape),
                                 dtype=_STATE_DTYPES[g.need.dtype], device=self.device)
             else:
                 raise TypeError(f"unknown cache need {g.need!r}")
@@ -393,18 +415,11 @@ class ModelRunner:
             slot_of_token = page_of_token * ps + positions % ps
             np.maximum(table, 0, out=table)
             sections += [table.reshape(-1), slot_of_token]
-        decode_list = np.flatnonzero(q_lens == 1)
-        sections.append(decode_list)
         sections.append(np.asarray(row_slots, dtype=np.int64))
-        for r, skip_decode in [(r, False) for r in self.tile_rows] + [(r, True) for r in self.prefill_tile_rows]:
-            n_tiles = (q_lens + r - 1) // r
-            if skip_decode:
-                n_tiles = np.where(q_lens == 1, 0, n_tiles)
-            tile_entry = np.repeat(np.arange(B), n_tiles)
-            first = np.zeros(B, dtype=np.int64)
-            np.cumsum(n_tiles[:-1], out=first[1:])
-            tile_q0 = (np.arange(int(n_tiles.sum())) - first[tile_entry]) * r
-            sections += [tile_entry, tile_q0]
+        shape = StepShape(q_lens, pos0, cu_q, kv_len, slots)
+        built = [(need, need.build(shape)) for need in self.index_needs]
+        for _need, arrays in built:
+            sections += [np.asarray(a) for a in arrays]
 
         idx, host = self._staging.next_host()
         offsets: List[Tuple[int, int]] = []
@@ -424,17 +439,15 @@ class ModelRunner:
         for _ in self.layout.paged_groups():
             table = next(it).view(B, max_blocks)
             groups.append(GroupStep(table, next(it)))
-        decode_entries = next(it)
         self.last_want_slots = next(it)
-        tiles = {r: (next(it), next(it)) for r in self.tile_rows}
-        prefill_tiles = {r: (next(it), next(it)) for r in self.prefill_tile_rows}
+        indices = {need.key: tuple(next(it) for _ in arrays) for need, arrays in built}
         host_entries = [HostEntry(e.request_id, int(slots[i]), int(q_lens[i]), int(pos0[i]))
                         for i, e in enumerate(entries)]
         step = StepContext(
             num_tokens=T, num_entries=B, token_ids=views[0], positions=views[1], cu_q=views[2],
-            kv_len=views[3], state_slots=views[4], groups=groups, tiles=tiles, entries=host_entries,
+            kv_len=views[3], state_slots=views[4], groups=groups, entries=host_entries,
             max_q_len=int(q_lens.max()), max_kv_len=int(kv_len.max()), decode_only=bool((q_lens == 1).all()),
-            decode_entries=decode_entries, num_decode=int(decode_list.size), prefill_tiles=prefill_tiles)
+            indices=indices)
         return step, (views[5] if rows else None)
 
     # --------------------------------------------------------------------------- step

@@ -162,7 +162,7 @@ class ChainedDecoder:
     def forward(self, step: StepContext, caches: List, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         d, T, sms = self.d, step.num_tokens, self.ctx.num_sms
         h = self.h[:T]
-        K.embed_gather(step.token_ids[:T], d.embed_table, h)
+        d.embed.forward(step, h)
         chains = self._chains(T, step, caches)
         K.decode_chain(chains[0][0], chains[0][1], T, sms)
         for i, (block, _) in enumerate(self.entries):
@@ -174,4 +174,4 @@ class ChainedDecoder:
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         n = d.final_norm.add_norm(h, None, rows=logit_rows)
-        return d.head(n, out_dtype=torch.float32)
+        return d.head.forward(n)

@@ -1,5 +1,5 @@
-"""A decoder put together from a `ModelSpec`: embedding, the blocks in their run order,
-final norm over the wanted rows, head.  It owns no sizes of its own; everything comes
+"""A decoder put together from a `ModelSpec`: the stem (an embedding part), the blocks in
+their run order, final norm over the wanted rows, the tail (a head part).  It owns no sizes of its own; everything comes
 from the spec (crates/infer-worker/src/models/decoder.rs:57-200 is the reference's
 `Decoder` with `embed / decode_layers / finalize`).
 """
@@ -9,11 +9,9 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..ops import kernels as K
-from ..parts import attention, ffn, norm, rope  # noqa: F401  (registers the built-in parts)
-from ..parts.base import NORMS, BuildContext, CacheNeed, ParamDecl, StepContext
+from ..parts import attention, ffn, norm, rope, stem_tail  # noqa: F401  (registers the built-in parts)
+from ..parts.base import EMBEDDINGS, HEADS, NORMS, BuildContext, CacheNeed, ParamDecl, StepContext, StepIndex
 from ..parts.block import Block, Hidden
-from ..parts.linear import Linear
 from ..parts.spec import ModelSpec
 
 
@@ -23,9 +21,8 @@ class Decoder:
         self.spec = spec
         self.blocks: List[Block] = [Block(ls) for ls in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm)
-        self.embed_table: Optional[torch.Tensor] = None
-        self.head: Optional[Linear] = None
-        self.head_is_tied = False
+        self.embed = EMBEDDINGS.build(spec.embed_spec())
+        self.head = HEADS.build(spec.head_spec())
         self.chained = None
         for i, e in enumerate(spec.run_order):
             mixer = self.blocks[e.layer].mixer
@@ -39,12 +36,11 @@ class Decoder:
     def param_decls(self) -> Dict[str, ParamDecl]:
         """Full tensor name -> declaration, for the loader and the random-weights mode."""
         s = self.spec
-        decls: Dict[str, ParamDecl] = {
-            s.embed_name + "weight": ParamDecl((s.vocab_size, s.hidden_size)),
-            s.head_name + "weight": ParamDecl((s.vocab_size, s.hidden_size), optional=s.tie_head),
-        }
-        for name, d in self.final_norm.param_decls().items():
-            decls[s.final_norm_name + name] = d
+        decls: Dict[str, ParamDecl] = {}
+        for prefix, part in ((s.embed_name, self.embed), (s.head_name, self.head),
+                             (s.final_norm_name, self.final_norm)):
+            for name, d in part.param_decls().items():
+                decls[prefix + name] = d
         for block, ls in zip(self.blocks, s.layers):
             for role, part in block.roles().items():
                 for name, d in part.param_decls().items():
@@ -55,17 +51,14 @@ class Decoder:
         """Per run entry: (layer, what its mixer keeps between steps, entry whose cache it reads)."""
         return [(e.layer, self.blocks[e.layer].mixer.cache_need(), e.cache_of) for e in self.spec.run_order]
 
-    def attention_tile_rows(self) -> Tuple[int, ...]:
-        rows = set()
+    def step_indices(self) -> List[StepIndex]:
+        """The index arrays the model's parts want made for every step, each key once."""
+        seen: Dict = {}
         for b in self.blocks:
-            rows.update(b.mixer.attention_tile_rows)
-        return tuple(sorted(rows))
-
-    def prefill_tile_rows(self) -> Tuple[int, ...]:
-        rows = set()
-        for b in self.blocks:
-            rows.update(b.mixer.prefill_tile_rows)
-        return tuple(sorted(rows))
+            for part in (b.mixer, b.ffn):
+                for need in part.step_indices():
+                    seen.setdefault(need.key, need)
+        return list(seen.values())
 
     @property
     def graph_safe(self) -> bool:
@@ -74,18 +67,20 @@ class Decoder:
     # ------------------------------------------------------------------------- build
     def prepare(self, ctx: BuildContext) -> None:
         self.ctx = ctx
+        self.embed.prepare(ctx)
         for b in self.blocks:
             b.prepare(ctx)
         self.final_norm.prepare(ctx)
+        self.head.prepare(ctx)
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
-        self.embed_table = tensors[s.embed_name + "weight"].contiguous()
-        head = tensors.get(s.head_name + "weight")
-        # the head is the embedding table when the file has no head of its own
+        pick = lambda prefix, part: {n: tensors[prefix + n] for n in part.param_decls() if prefix + n in tensors}
+        self.embed.load(pick(s.embed_name, self.embed))
+        # a head without a weight of its own in the file takes what the embedding offers to share
         # (crates/infer-worker/src/models/decoder.rs:245-262)
-        self.head_is_tied = head is None
-        self.head = Linear(self.embed_table if head is None else head, self.ctx.num_sms)
+        self.head.offer_shared(self.embed.shared_table())
+        self.head.load(pick(s.head_name, self.head))
         self.final_norm.load({n: tensors[s.final_norm_name + n] for n in self.final_norm.param_decls()})
         for block, ls in zip(self.blocks, s.layers):
             for role, part in block.roles().items():
@@ -103,11 +98,11 @@ class Decoder:
         if self.chained is not None and self.chained.takes(step):
             return self.chained.forward(step, caches, logit_rows)
         h = torch.empty((step.num_tokens, s.hidden_size), dtype=torch.float32, device=self.ctx.device)
-        K.embed_gather(step.token_ids[: step.num_tokens], self.embed_table, h)
+        self.embed.forward(step, h)
         hidden = Hidden(h, None)
         for i, e in enumerate(s.run_order):
             self.blocks[e.layer].forward(hidden, step, caches[i])
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         n = self.final_norm.add_norm(hidden.stream, hidden.pending, rows=logit_rows)
-        return self.head(n, out_dtype=torch.float32)
+        return self.head.forward(n)

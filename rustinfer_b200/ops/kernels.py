@@ -68,19 +68,21 @@ def residual_add(h: torch.Tensor, delta: torch.Tensor) -> None:
           "residual_add")
 
 
-def rope_scatter(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
-                 slot_of_token: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+def rope_scatter(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torch.Tensor],
+                 sin: Optional[torch.Tensor], slot_of_token: Optional[torch.Tensor], cache: Optional[torch.Tensor],
                  num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int) -> None:
     """Rotate q (in place) and k of qkv [T, (Hq+2Hkv)*hd]; write k,v of token t into the
-    cache [pages, 2, Hkv, page, hd] at slot_of_token[t] (page*page_size + offset; <0 skips)."""
+    cache [pages, 2, Hkv, page, hd] at slot_of_token[t] (page*page_size + offset; <0 skips).
+    With rotary_dim 0 (cos and sin None) nothing is rotated: k and v are only written."""
     require_cuda(qkv, positions, cos, sin, slot_of_token, cache)
     _i32(positions, "positions"); _i32(slot_of_token, "slot_of_token")
     T = qkv.shape[0]
     if qkv.stride(1) != 1 or qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
         raise KernelError("rope_scatter: qkv must be [T, (Hq+2Hkv)*head_dim] with unit column stride")
-    if rotary_dim % 2 or not 0 < rotary_dim <= head_dim:
+    if rotary_dim % 2 or not 0 <= rotary_dim <= head_dim:
         raise KernelError(f"rope_scatter: rotary_dim {rotary_dim} must be even and at most head_dim")
-    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape[1] != rotary_dim // 2:
+    if rotary_dim and (cos is None or sin is None or cos.dtype != torch.float32 or sin.dtype != torch.float32
+                       or cos.shape[1] != rotary_dim // 2):
         raise KernelError("rope_scatter: cos/sin are fp32 [positions, rotary_dim/2]")
     page = 0
     if cache is not None:
@@ -150,10 +152,11 @@ def gemm_tc_error(device: torch.device) -> int:
     return code
 
 
-def gemm_tc_plan(M: int, N: int, K: int, num_sms: int = 148, epilogue: int = EPI_BF16):
+def gemm_tc_plan(M: int, N: int, K: int, num_sms: Optional[int] = None, epilogue: int = EPI_BF16):
     """(swap, bn, splits, a_box): which operand sits on the 128-row side of the MMA, the
     tile of the other one, how many K slices, and how many rows of the 128 a tile really
     covers, so that about one even wave of CTAs covers the GPU."""
+    num_sms = num_sms or L.num_sms()
     if M <= 64:
         swap, bn = 1, (16 if M <= 16 else 32 if M <= 32 else 64)
         tiles = -(-N // 128)
@@ -180,7 +183,7 @@ def gemm_tc_supports(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_BF16,
-            plan=None, num_sms: int = 148) -> None:
+            plan=None, num_sms: Optional[int] = None) -> None:
     """out = x[M,K] @ w[N,K]^T on the tcgen05 tensor cores, bf16 inputs, fp32 accumulation.
     epilogue: EPI_BF16 / EPI_F32 store into out [M,N]; EPI_SILU stores silu(gate)*up into
     out [M,N/2] for a weight whose rows alternate gate_j, up_j; EPI_RESIDUAL adds into the

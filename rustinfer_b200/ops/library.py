@@ -163,6 +163,20 @@ def require_cuda(*tensors: Optional[torch.Tensor]) -> None:
             raise KernelError("the sm_100a kernels take CUDA tensors only; there is no CPU path")
 
 
+_sms: Dict[int, int] = {}
+
+
+def num_sms(device=None) -> int:
+    """Streaming multiprocessors of a CUDA device (the current one by default), asked of the device."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    n = _sms.get(index)
+    if n is None:
+        n = _sms[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return n
+
+
 def stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 

@@ -14,7 +14,7 @@ import torch
 from ..ops import kernels as K
 from ..ops import library as L
 from .base import (BuildContext, Mixer, PagedKV, PagedLayerCache, ParamDecl, POSITIONS, StepContext,
-                   register_mixer)
+                   register_mixer, single_token_entries, token_tiles)
 from .linear import Linear
 from .spec import PartSpec
 
@@ -70,8 +70,9 @@ class GQAAttention(Mixer):
         if self.use_mma:
             self.tokens_per_tile = (K.tc_tokens_per_tile(self.Hq, self.Hkv) if self.use_tc
                                     else K.mma_tokens_per_tile(self.Hq, self.Hkv))
-            self.attention_tile_rows = ()
-            self.prefill_tile_rows = (self.tokens_per_tile,)
+            # entries of one token go to the split-KV kernel, the others are cut into tiles
+            self._single = single_token_entries()
+            self._tiles = token_tiles(self.tokens_per_tile, skip_single_token=True)
             key = ("decode_scratch", self.Hq, self.hd)
             if key not in ctx.shared:
                 no, nl = K.decode_scratch_floats(ctx.max_batch_seqs, self.Hq, self.hd, self.MAX_SPLITS)
@@ -84,8 +85,8 @@ class GQAAttention(Mixer):
                                        or int(lib.ri_attention_decode_ctas_per_sm()))
             self.decode_tile_keys = int(lib.ri_attention_decode_tile_keys())
         else:
-            self.attention_tile_rows = (16,)
-            self.prefill_tile_rows = ()
+            self._single = None
+            self._tiles = token_tiles(16, skip_single_token=False)
         if self.position_spec is not None:
             key = ("position", self.position_spec.key(), ctx.max_model_len)
             if key not in ctx.shared:
@@ -93,6 +94,9 @@ class GQAAttention(Mixer):
                 part.prepare(ctx)
                 ctx.shared[key] = part
             self.position = ctx.shared[key]
+
+    def step_indices(self):
+        return [self._tiles] if self._single is None else [self._single, self._tiles]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         # q, k, v fused by rows into one matrix, gate rows first
@@ -121,8 +125,10 @@ class GQAAttention(Mixer):
                            self.position.sin, g.slot_of_token if writes else None,
                            cache.kv if writes else None, self.Hq, self.Hkv if writes else 0, self.hd,
                            self.position.rotary_dim)
-        else:
-            raise NotImplementedError("attention without a rotary encoding has no cache-write kernel yet")
+        elif writes:
+            # no position encoding inside the mixer: keys and values go into their pages as they are
+            K.rope_scatter(qkv, step.positions, None, None, g.slot_of_token, cache.kv, self.Hq, self.Hkv,
+                           self.hd, 0)
         return self._project_out(self.attend(qkv[:, : self.Hq * self.hd], step, cache), residual)
 
     def attend(self, q: torch.Tensor, step: StepContext, cache: PagedLayerCache,
@@ -134,16 +140,17 @@ class GQAAttention(Mixer):
         if out is None:
             out = torch.empty((T, self.Hq * self.hd), dtype=self.ctx.dtype, device=q.device)
         if not self.use_mma:
-            tile_entry, tile_q0 = step.tiles[16]
+            tile_entry, tile_q0 = step.index(self._tiles)
             K.attention_plain(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_q0,
                               self.Hq, self.Hkv, self.hd, self.scale, self.window)
             return out
-        if step.num_decode:
-            splits = self._splits(step.num_decode, step.max_kv_len)
+        (single,) = step.index(self._single)
+        if single.numel():
+            splits = self._splits(single.numel(), step.max_kv_len)
             K.attention_decode_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len,
-                                    step.decode_entries, step.num_decode, self.Hq, self.Hkv, self.hd,
+                                    single, single.numel(), self.Hq, self.Hkv, self.hd,
                                     self.scale, self.window, splits, self.part_o, self.part_lse)
-        tile_entry, tile_tok0 = step.prefill_tiles[self.tokens_per_tile]
+        tile_entry, tile_tok0 = step.index(self._tiles)
         if tile_entry.numel():
             prefill = K.attention_prefill_tc if self.use_tc else K.attention_prefill_bf16
             prefill(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len, tile_entry, tile_tok0,

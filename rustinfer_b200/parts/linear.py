@@ -16,12 +16,12 @@ from ..ops import kernels as K
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, num_sms: int = 148):
+    def __init__(self, weight: torch.Tensor, num_sms: Optional[int] = None):
         if weight.dim() != 2:
             raise ValueError("a linear weight is a matrix [out, in]")
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
-        self.num_sms = num_sms
+        self.num_sms = num_sms          # None: the kernel front asks the device
         # bf16 weights whose rows are 16-byte multiples run on this engine's tcgen05 kernel
         self.tensor_core = (self.weight.dtype == torch.bfloat16 and self.weight.is_cuda
                             and self.in_features % 8 == 0)

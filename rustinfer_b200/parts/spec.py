@@ -68,6 +68,18 @@ class ModelSpec:
     head_name: str
     tie_head: bool                      # config says the head is the embedding table
     eos_token_ids: Tuple[int, ...] = ()
+    # the stem and the tail, chosen like every other part; None: a plain token embedding and a
+    # linear head of the model's sizes
+    embed: Optional[PartSpec] = None
+    head: Optional[PartSpec] = None
+
+    def embed_spec(self) -> PartSpec:
+        return self.embed or PartSpec("token_embedding", {"vocab_size": self.vocab_size,
+                                                          "hidden_size": self.hidden_size})
+
+    def head_spec(self) -> PartSpec:
+        return self.head or PartSpec("linear_head", {"vocab_size": self.vocab_size,
+                                                     "hidden_size": self.hidden_size, "tied": self.tie_head})
 
     def validate(self) -> None:
         n = len(self.layers)

@@ -30,7 +30,31 @@ TINY_C = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden
               rope_scaling=dict(rope_type="llama3", factor=4.0, low_freq_factor=1.0,
                                 high_freq_factor=2.0, original_max_position_embeddings=32),
               rms_norm_eps=3e-6, tie_word_embeddings=True, max_position_embeddings=256)
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Three more whose head sizes are 64 and 128: the attention kernels that serve the benchmark
+# shapes (keys and values fetched by TMA for decoding, tcgen05 for prompt portions) take only
+# those, so whole-model comparisons reach them through these.  D: groups of 4 (tcgen05 prompt
+# attention, TMA decode); E: groups of 3 (rows of a tile do not fill it evenly); F: one kv head,
+# heads*head_dim != hidden.
+TINY_D = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2,
+              hidden_size=256, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+              intermediate_size=512, vocab_size=1000, rope_theta=500000.0,
+              rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0,
+                                high_freq_factor=4.0, original_max_position_embeddings=256),
+              rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024)
+TINY_E = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=2,
+              hidden_size=384, num_attention_heads=6, num_key_value_heads=2, head_dim=128,
+              intermediate_size=520, vocab_size=777, rope_theta=500000.0,
+              rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                high_freq_factor=4.0, original_max_position_embeddings=128),
+              rms_norm_eps=2e-6, tie_word_embeddings=False, max_position_embeddings=1024)
+TINY_F = dict(architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=3,
+              hidden_size=192, num_attention_heads=4, num_key_value_heads=1, head_dim=128,
+              intermediate_size=328, vocab_size=515, rope_theta=10000.0, rope_scaling=None,
+              rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=1024)
+# B with the feed-forward width and vocabulary that are powers of two times three (256, 384),
+# beside the odd ones above
+TINY_BS = dict(TINY_B, intermediate_size=256, vocab_size=384)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F, "Bs": TINY_BS}
 
 
 def tensor_shapes(cfg: dict) -> Dict[str, tuple]:

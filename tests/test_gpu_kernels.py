@@ -660,14 +660,14 @@ def test_argmax_lowest_index_wins(V):
     assert out.tolist() == want and out[1] == 7 and out[2] == 0 and out[3] == V - 1
 
 
-@pytest.mark.parametrize("V", [130, 391, 5000])
+@pytest.mark.parametrize("V", [130, 391, 5000, 128256])
 def test_sample_matches_the_plain_sampler(V):
     g = torch.Generator().manual_seed(V)
     combos = [(0.8, 0, 1.0, 0.0), (1.0, 5, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
               (0.9, 40, 0.8, 0.01), (0.0, 0, 1.0, 0.0), (1.0, 1, 1.0, 0.0), (1.0, 0, 0.0, 0.0),
               (2.0, 3, 0.5, 0.2)]
     rows = []
-    for rep in range(4):
+    for rep in range(4 if V < 100000 else 2):
         for c in combos:
             rows.append(c)
     R = len(rows)

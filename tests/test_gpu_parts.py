@@ -32,21 +32,23 @@ def ctx(dtype, max_len=256, page=8):
     return BuildContext(dev(), dtype, max_len, page)
 
 
-def one_sequence_step(T, page, n_groups=1, prefill_rows=()):
-    """A StepContext for one whole sequence of T tokens laid out in pages 3, 4, 5, ..."""
-    from rustinfer_b200.parts.base import GroupStep, HostEntry, StepContext
+def one_sequence_step(T, page, n_groups=1, needs=()):
+    """A StepContext for one whole sequence of T tokens laid out in pages 3, 4, 5, ..., with
+    the index arrays the part under test declares (`needs`: its step_indices())."""
+    import numpy as np
+    from rustinfer_b200.parts.base import GroupStep, HostEntry, StepContext, StepShape
     i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())
     blocks = (T + page - 1) // page
     table = i32([[3 + b for b in range(blocks)]])
     slot = i32([(3 + t // page) * page + t % page for t in range(T)])
-    tiles = {16: (i32([0] * ((T + 15) // 16)), i32(list(range(0, T, 16))))}
+    a64 = lambda x: np.asarray(x, dtype=np.int64)
+    shape = StepShape(a64([T]), a64([0]), a64([0, T]), a64([T]), a64([0]))
+    indices = {n.key: tuple(i32(arr.tolist()) for arr in n.build(shape)) for n in needs}
     return StepContext(num_tokens=T, num_entries=1, token_ids=i32([0] * T), positions=i32(list(range(T))),
                        cu_q=i32([0, T]), kv_len=i32([T]), state_slots=i32([0]),
-                       groups=[GroupStep(table, slot) for _ in range(n_groups)], tiles=tiles,
+                       groups=[GroupStep(table, slot) for _ in range(n_groups)],
                        entries=[HostEntry("x", 0, T, 0)], max_q_len=T, max_kv_len=T, decode_only=False,
-                       decode_entries=i32([]), num_decode=0,
-                       prefill_tiles={r: (i32([0] * ((T + r - 1) // r)), i32(list(range(0, T, r))))
-                                      for r in prefill_rows})
+                       indices=indices)
 
 
 @pytest.mark.parametrize("dt", DT)
@@ -133,7 +135,7 @@ def test_attention_part(dt, Hq, Hkv, hd, window):
     part.load({n: t.to(dev()) for n, t in w.items()})
     x = torch.randn(T, d).to(dt)
     cache = torch.full((12, 2, Hkv, page, hd), float("nan"), dtype=dt, device=dev())
-    y = part.forward(x.to(dev()), one_sequence_step(T, page, prefill_rows=part.prefill_tile_rows),
+    y = part.forward(x.to(dev()), one_sequence_step(T, page, needs=part.step_indices()),
                      PagedLayerCache(cache, 0, True))
     xd, wd = x.double(), {n: t.double() for n, t in w.items()}
     f = P.rope_inv_freq(hd, 10000.0, None)
@@ -369,3 +371,248 @@ def test_run_order_shared_cache_and_window_group(tmp_path, dtype):
         r.close("a")
         r.cache.check_invariants()
     assert r.cache.free_pages() == {0: 40, 1: 40}
+
+
+# ------------------------------------------------ toy parts of every kind, from this file alone
+# A stem with a multiplier and learned positions, a head with a soft cap, another rotary law, a
+# feed-forward that routes each token to one of three experts, attention without any position
+# encoding, and a mixer with fixed-size state that is safe to capture: it declares an index
+# array of its own, which the step builder makes for every step and every replay.  None of
+# them is a part of any real model; they show what the interfaces carry.
+
+def _register_zoo():
+    import numpy as np
+    from rustinfer_b200.config.registry import ArchitectureFamily, register_architecture
+    from rustinfer_b200.parts.base import (Embedding, FeedForward, FixedState, Head, Mixer, ParamDecl,
+                                           PositionEncoding, StepIndex, register_embedding,
+                                           register_feed_forward, register_head, register_mixer,
+                                           register_position)
+    from rustinfer_b200.parts.linear import Linear
+    from rustinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+    @register_embedding("zoo_scaled_positions")
+    class ScaledWithPositions(Embedding):
+        def __init__(self, params):
+            super().__init__(params)
+            self.V, self.d = int(params["vocab_size"]), int(params["hidden_size"])
+            self.mult, self.max_pos = float(params["multiplier"]), int(params["max_positions"])
+
+        def param_decls(self):
+            return {"weight": ParamDecl((self.V, self.d)), "positions.weight": ParamDecl((self.max_pos, self.d))}
+
+        def load(self, tensors):
+            self.table, self.pos = tensors["weight"], tensors["positions.weight"]
+
+        def shared_table(self):
+            return self.table
+
+        def forward(self, step, h):
+            T = step.num_tokens
+            ids, pos = step.token_ids[:T].long(), step.positions[:T].long()
+            h.copy_(self.table[ids].float() * self.mult + self.pos[pos].float())
+
+    @register_head("zoo_capped")
+    class CappedHead(Head):
+        def __init__(self, params):
+            super().__init__(params)
+            self.V, self.d, self.cap = int(params["vocab_size"]), int(params["hidden_size"]), float(params["cap"])
+
+        def param_decls(self):
+            return {"weight": ParamDecl((self.V, self.d), optional=True)}
+
+        def load(self, tensors):
+            self.linear = Linear(tensors.get("weight", self.shared))
+
+        def forward(self, normed):
+            return self.cap * torch.tanh(self.linear(normed, out_dtype=torch.float32) / self.cap)
+
+    @register_position("zoo_stretched_rope")
+    class StretchedRope(PositionEncoding):
+        """angle = (position / stretch) * theta^(-2i/d): another frequency law behind the same tables."""
+        def __init__(self, params):
+            super().__init__(params)
+            self.rotary_dim, self.theta, self.stretch = int(params["head_dim"]), float(params["theta"]), float(params["stretch"])
+
+        def prepare(self, ctx):
+            super().prepare(ctx)
+            f = torch.tensor([self.theta ** (-2.0 * i / self.rotary_dim) for i in range(self.rotary_dim // 2)],
+                             dtype=torch.float64)
+            ang = (torch.arange(ctx.max_model_len, dtype=torch.float64) / self.stretch)[:, None] * f[None, :]
+            self.cos, self.sin = torch.cos(ang).float().to(ctx.device), torch.sin(ang).float().to(ctx.device)
+
+    phase = StepIndex(("zoo_phase",), lambda sh: (sh.pos0 % 3,), lambda max_tokens, max_entries: max_entries + 4,
+                      depends_on_positions=True)
+
+    @register_mixer("zoo_moving_sum")
+    class MovingSumOnDevice(Mixer):
+        """s_t = decay * s_{t-1} + (1 + 0.25 * (position mod 3)) * x_t; y_t = W s_t.  Steps of single
+        tokens read only device tensors (the state rows by slot, the phase from the index array it
+        declared), so they can be captured."""
+        graph_safe = True
+
+        def __init__(self, params):
+            super().__init__(params)
+            self.d, self.decay = int(params["hidden_size"]), float(params["decay"])
+
+        def param_decls(self):
+            return {"mix.weight": ParamDecl((self.d, self.d))}
+
+        def cache_need(self):
+            return FixedState((self.d,), "float32")
+
+        def step_indices(self):
+            return [phase]
+
+        def load(self, tensors):
+            self.mix = Linear(tensors["mix.weight"])
+
+        def forward(self, x, step, cache):
+            if step.decode_only:
+                n = step.num_entries
+                slots = step.state_slots[:n].long()
+                (ph,) = step.index(phase)
+                s = self.decay * cache.state[slots] + (1 + 0.25 * ph[:n].float())[:, None] * x.float()
+                cache.state.index_copy_(0, slots, s)
+                return self.mix(s.to(x.dtype), out_dtype=x.dtype)
+            states = torch.empty((x.shape[0], self.d), dtype=torch.float32, device=x.device)
+            row = 0
+            for e in step.entries:
+                s = cache.state[e.slot]
+                for j in range(e.q_len):
+                    s = self.decay * s + (1 + 0.25 * ((e.pos0 + j) % 3)) * x[row + j].float()
+                    states[row + j] = s
+                cache.state[e.slot] = s
+                row += e.q_len
+            return self.mix(states.to(x.dtype), out_dtype=x.dtype)
+
+    @register_feed_forward("zoo_routed")
+    class RoutedToy(FeedForward):
+        """Each token goes to the expert with the largest router logit (fp32): down_e(relu(up_e(x)))."""
+        def __init__(self, params):
+            super().__init__(params)
+            self.d, self.inter, self.E = int(params["hidden_size"]), int(params["intermediate_size"]), int(params["experts"])
+
+        def param_decls(self):
+            d = {"router.weight": ParamDecl((self.E, self.d))}
+            for e in range(self.E):
+                d[f"experts.{e}.up.weight"] = ParamDecl((self.inter, self.d))
+                d[f"experts.{e}.down.weight"] = ParamDecl((self.d, self.inter))
+            return d
+
+        def load(self, tensors):
+            self.router = Linear(tensors["router.weight"])
+            self.up = [Linear(tensors[f"experts.{e}.up.weight"]) for e in range(self.E)]
+            self.down = [Linear(tensors[f"experts.{e}.down.weight"]) for e in range(self.E)]
+
+        def forward(self, x, step):
+            pick = self.router(x, out_dtype=torch.float32).argmax(dim=1)
+            out = torch.zeros_like(x)
+            for e in range(self.E):
+                y = self.down[e](torch.relu(self.up[e](x)), out_dtype=x.dtype)
+                out += y * (pick == e)[:, None].to(x.dtype)
+            return out
+
+    def spec_of(cfg):
+        d, hd = cfg["hidden_size"], 16
+        norm = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+        swiglu = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": cfg["intermediate_size"]})
+        routed = PartSpec("zoo_routed", {"hidden_size": d, "intermediate_size": cfg["intermediate_size"], "experts": 3})
+        att = lambda pos: PartSpec("gqa_attention", {"hidden_size": d, "num_heads": d // hd, "num_kv_heads": 2,
+                                                     "head_dim": hd, "scale": 0.25, "window": None, "position": pos})
+        stretched = PartSpec("zoo_stretched_rope", {"head_dim": hd, "theta": 1000.0, "stretch": 2.5})
+        mixers = [att(None), PartSpec("zoo_moving_sum", {"hidden_size": d, "decay": 0.7}), att(stretched)]
+        ffns = [swiglu, routed if cfg["routed"] else swiglu, swiglu]
+        layers = tuple(LayerSpec(mixer=m, mixer_norm=norm, ffn=f, ffn_norm=norm,
+                                 names={"mixer": f"l{i}.mix.", "mixer_norm": f"l{i}.n1.", "ffn": f"l{i}.ffn.",
+                                        "ffn_norm": f"l{i}.n2."}) for i, (m, f) in enumerate(zip(mixers, ffns)))
+        return ModelSpec(hidden_size=d, vocab_size=cfg["vocab_size"], layers=layers,
+                         run_order=tuple(RunEntry(i) for i in range(3)), final_norm=norm, embed_name="embed.",
+                         final_norm_name="norm.", head_name="head.", tie_head=True,
+                         embed=PartSpec("zoo_scaled_positions", {"vocab_size": cfg["vocab_size"], "hidden_size": d,
+                                                                 "multiplier": 1.5, "max_positions": 128}),
+                         head=PartSpec("zoo_capped", {"vocab_size": cfg["vocab_size"], "hidden_size": d, "cap": 3.0}))
+
+    register_architecture(["ZooLM"], ArchitectureFamily("zoo", lambda c, g: dict(c), spec_of))
+
+
+def _zoo_plain(cfg, w, ids):
+    d, hd, Hkv = cfg["hidden_size"], 16, 2
+    Hq, T = d // hd, len(ids)
+    pos = torch.arange(T)
+    h = P.embedding(w["embed.weight"], ids) * 1.5 + w["embed.positions.weight"][:T]
+    for i in range(3):
+        p = f"l{i}."
+        x = P.rmsnorm(h, w[p + "n1.weight"], 1e-5)
+        if i == 1:
+            s, rows = torch.zeros(d, dtype=torch.float64), []
+            for t in range(T):
+                s = 0.7 * s + (1 + 0.25 * (t % 3)) * x[t]
+                rows.append(s)
+            h = h + torch.stack(rows) @ w[p + "mix.mix.weight"].T
+        else:
+            q = (x @ w[p + "mix.q_proj.weight"].T).view(T, Hq, hd)
+            k = (x @ w[p + "mix.k_proj.weight"].T).view(T, Hkv, hd)
+            v = (x @ w[p + "mix.v_proj.weight"].T).view(T, Hkv, hd)
+            if i == 2:
+                f = torch.tensor([1000.0 ** (-2.0 * j / hd) for j in range(hd // 2)], dtype=torch.float64)
+                q, k = P.rope_rotate(q, pos / 2.5, f), P.rope_rotate(k, pos / 2.5, f)
+            h = h + P.causal_gqa_attention(q, k, v, 0.25).reshape(T, d) @ w[p + "mix.o_proj.weight"].T
+        x = P.rmsnorm(h, w[p + "n2.weight"], 1e-5)
+        if i == 1 and cfg["routed"]:
+            pick = (x @ w[p + "ffn.router.weight"].T).argmax(dim=1)
+            y = torch.zeros_like(x)
+            for t in range(T):
+                e = int(pick[t])
+                y[t] = torch.relu(x[t] @ w[p + f"ffn.experts.{e}.up.weight"].T) @ w[p + f"ffn.experts.{e}.down.weight"].T
+            h = h + y
+        else:
+            m = P.swiglu(x @ w[p + "ffn.gate_proj.weight"].T, x @ w[p + "ffn.up_proj.weight"].T)
+            h = h + m @ w[p + "ffn.down_proj.weight"].T
+    z = P.rmsnorm(h, w["norm.weight"], 1e-5) @ w["embed.weight"].T
+    return 3.0 * torch.tanh(z / 3.0)
+
+
+@pytest.mark.parametrize("dtype,routed", [("float32", True), ("float32", False), ("bfloat16", False)])
+def test_toy_parts_of_every_kind_are_registered_built_stepped_and_captured(tmp_path, dtype, routed):
+    """Stem, head, position law, routed feed-forward, attention without positions and a stateful
+    mixer with an index array of its own, all defined above; stepped eagerly and from captured
+    graphs whose bucket is larger than the batch (padding rows must not touch a live request's
+    state), against the float64 statement."""
+    from rustinfer_b200.engine.runner import ModelRunner, StepEntry
+    from rustinfer_b200.weights.random_init import write_random_model
+    _register_zoo()
+    cfg = {"architectures": ["ZooLM"], "hidden_size": 64, "intermediate_size": 80, "vocab_size": 101, "routed": routed}
+    folder = write_random_model(str(tmp_path / "zoo"), cfg, seed=9, std=0.15, norm_std=0.2)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    _, w = P.read_model_folder(folder)
+    assert "head.weight" not in w and "embed.positions.weight" in w
+    g = torch.Generator().manual_seed(2)
+    seqs = [torch.randint(0, 101, (n,), generator=g).tolist() for n in (37, 50, 44)]
+    refs = [_zoo_plain(cfg, w, s) for s in seqs]
+    tol = LOGITS_TOL[dtype]
+    for sizes in (None, [1, 2, 4]):
+        r = ModelRunner(folder, dtype=dtype, max_model_len=96, page_size=8, num_pages=40, max_batch_seqs=4,
+                        max_batch_tokens=96, capture_sizes=sizes)
+        assert r.model.graph_safe and r.use_graphs == (sizes is not None)
+        assert ("zoo_phase",) in [n.key for n in r.index_needs]
+        got = [[] for _ in seqs]
+        first = [9, 20, 3]
+        for i, s in enumerate(seqs):
+            r.open(i)
+            got[i].append(r.step([StepEntry(i, s[: first[i]], list(range(first[i])))]))
+        at = list(first)
+        turn = 0
+        while any(a < len(s) for a, s in zip(at, seqs)):
+            live = [i for i in range(3) if at[i] < len(seqs[i]) and (turn + i) % 5 != 4]
+            turn += 1
+            if not live:
+                continue
+            lg = r.step([StepEntry(i, [seqs[i][at[i]]], [0]) for i in live])   # 1 to 3 rows: buckets 1, 2, 4
+            for k_, i in enumerate(live):
+                got[i].append(lg[k_: k_ + 1])
+                at[i] += 1
+        if sizes is not None:
+            assert r.graph_replays > 50 and 4 in r._graphs
+        for i in range(3):
+            assert rel_err(torch.cat(got[i]), refs[i]) <= tol, (dtype, sizes, i)

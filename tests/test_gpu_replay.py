@@ -32,8 +32,26 @@ TOL = {"float32": 2e-5, "bfloat16": 6e-2}
 # and the library picks GEMM tiles by batch size, so two cuts are two independent roundings;
 # each is held to TOL against the plain implementation, which is the comparison that counts.
 
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D", "E", "F", "Bs"]
+FAST = ["D", "E", "F"]                   # head sizes 64 and 128: the attention kernels of the benchmark shapes
 DTYPES = ["float32", "bfloat16"]
+PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16, "F": 8, "Bs": 8}
+
+
+def expect_fast_kernels(r, name):
+    """In bfloat16 the models with head sizes 64 and 128 must run on the kernels made for
+    them: keys and values by TMA when decoding, tcgen05 for prompt portions where the group
+    size lets it, and the chained products for steps of few tokens."""
+    if name not in FAST or r.dtype != torch.bfloat16:
+        return
+    from rustinfer_b200.ops import library
+    for b in r.model.blocks:
+        a = b.mixer
+        lib = library.attention_mma(a.hd)
+        tma = int(lib.ri_attention_decode_tma_ctas_per_sm(r.page_size))
+        assert tma > 0 and a.decode_ctas_per_sm == tma, "decode attention does not fetch by TMA"
+        assert a.use_tc == (128 % (a.Hq // a.Hkv) == 0), "prompt attention is not on tcgen05"
+    assert r.model.chained is not None and r.model.chained.max_tokens >= 16
 
 
 @pytest.fixture(scope="module")
@@ -41,7 +59,7 @@ def models(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
     for n in NAMES:
-        folder = make_sharp_model(str(root / n), n, seed=11 + ord(n))
+        folder = make_sharp_model(str(root / n), n, seed=11 + ord(n[0]) + len(n))
         out[n] = (folder, Plain(folder))
     return out
 
@@ -71,9 +89,10 @@ def run_cuts(r, rid, ids, cuts):
 def test_whole_tail_and_portions(models, name, dtype):
     folder, plain = models[name]
     V = TINY[name]["vocab_size"]
-    page = {"A": 16, "B": 8, "C": 16}[name]
+    page = PAGE[name]
     r = runner(folder, dtype, page=page)
-    for n, seed in [(100, 1), (70, 2), (33, 3)]:
+    expect_fast_kernels(r, name)
+    for n, seed in [(100, 1), (70, 2), (33, 3)] + ([(300, 5)] if name in FAST else []):
         ids = random_ids(n, V, seed)
         ref = plain.logits(ids)
         whole = run_cuts(r, "w", ids, [n])
@@ -113,7 +132,7 @@ def test_first_tokens_of_a_sequence(models, name, dtype):
 def test_long_decoding(models, name, dtype):
     folder, plain = models[name]
     V = TINY[name]["vocab_size"]
-    n = {"A": 128, "B": 400, "C": 250}[name]            # up to the model's own max positions
+    n = {"A": 128, "B": 400, "C": 250, "D": 300, "E": 200, "F": 200, "Bs": 100}[name]   # within the model's positions
     r = runner(folder, dtype, page=8)
     ids = random_ids(n, V, 4)
     got = run_cuts(r, "d", ids, [5] + [1] * (n - 5))
@@ -132,12 +151,13 @@ def test_mixed_batches_with_page_reuse(models, name, dtype):
     from rustinfer_b200.engine.runner import StepEntry
     folder, plain = models[name]
     V = TINY[name]["vocab_size"]
-    page = {"A": 16, "B": 8, "C": 4}[name]
+    page = {"A": 16, "B": 8, "C": 4, "D": 16, "E": 8, "F": 32, "Bs": 8}[name]
     lens = [41, 17, 64, 9, 52, 30, 23, 70]
     seqs = [random_ids(n, V, 100 + i) for i, n in enumerate(lens)]
     # room for the four largest neighbours, far less than the sum of all eight
     pool_tokens = 64 * 4
     r = runner(folder, dtype, max_tokens=pool_tokens, page=page, seqs=4)
+    expect_fast_kernels(r, name)
     got = {i: [] for i in range(len(seqs))}
     at = {i: 0 for i in range(len(seqs))}
     live, waiting = [], list(range(len(seqs)))
@@ -240,7 +260,7 @@ def test_trace_run_program(models, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E", "F"])
 def test_greedy_generation_through_the_entry_point(models, name, dtype):
     import plain_llama
     from rustinfer_b200.engine.engine import Engine
@@ -250,6 +270,7 @@ def test_greedy_generation_through_the_entry_point(models, name, dtype):
     prompts = [random_ids(n, V, 50 + n) for n in (5, 17, 32, 1)]
     eng = Engine(folder, dtype=dtype, max_batch_tokens=40, max_batch_seqs=3, max_model_len=64,
                  paged_block_size=8, chunked_prefill_size=24, num_blocks=20)
+    expect_fast_kernels(eng.runner, name)
     res = eng.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True))
     for p, out in zip(prompts, res):
         assert out.finish_reason == "length" and len(out.tokens) == 16
@@ -277,11 +298,31 @@ def test_seeded_sampling_does_not_depend_on_the_batch(models):
     eng = Engine(folder, dtype="float32", max_batch_tokens=64, max_batch_seqs=4, max_model_len=128,
                  paged_block_size=8, chunked_prefill_size=24)
     together = [r.tokens for r in eng.generate(prompts, sp)]
+    assert eng.stats.chained_steps > 0                        # drawn tokens stay in the device pipeline too
     alone = [eng.generate([p], sp)[0].tokens for p in prompts]
     assert together == alone
     other = [r.tokens for r in eng.generate(prompts, SamplingParams(temperature=0.8, seed=99, max_tokens=12,
                                                                    ignore_eos=True))]
     assert other != together
+    # and they are the tokens the plain sampler draws from the plain model's logits with the same
+    # uniform numbers: u(seed, position of the token being chosen), 53 bits of splitmix64 (the
+    # generator is written out here, not imported)
+    import plain_llama
+    M = (1 << 64) - 1
+
+    def draw(seed, position):
+        x = ((seed ^ ((position * 0x9E3779B97F4A7C15) & M)) + 0x9E3779B97F4A7C15) & M
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & M
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & M
+        return ((x ^ (x >> 31)) >> 11) / float(1 << 53)
+
+    plain = models["B"][1]
+    for p, got in zip(prompts, together):
+        seq = list(p)
+        for t in got:
+            row = plain.logits(seq)[-1]
+            assert t == plain_llama.sample_filtered(row, 0.8, 0, 1.0, 0.0, draw(1234, len(seq)))
+            seq.append(t)
 
 
 def test_preemption_recomputes_to_the_same_tokens(models):
@@ -300,17 +341,19 @@ def test_preemption_recomputes_to_the_same_tokens(models):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_decode_graphs_equal_eager_steps(models, dtype):
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_decode_graphs_equal_eager_steps(models, name, dtype):
     """Steps of single tokens replayed from a captured graph give the logits of the eager
     step: with rows that change owner, padding rows, a request id that returns with other
     pages, and token ids fed back on the device."""
     from rustinfer_b200.engine.runner import ModelRunner, StepEntry
-    folder, plain = models["B"]
-    V = TINY["B"]["vocab_size"]
+    folder, plain = models[name]
+    V = TINY[name]["vocab_size"]
     mk = lambda sizes: ModelRunner(folder, dtype=dtype, max_model_len=128, page_size=8, num_pages=48,
                                    max_batch_seqs=4, max_batch_tokens=128, capture_sizes=sizes)
     eager, graph = mk(None), mk([1, 2, 4])
     assert not eager.use_graphs and graph.use_graphs
+    expect_fast_kernels(graph, name)
     seqs = {i: random_ids(40 + 7 * i, V, 200 + i) for i in range(5)}
     for r in (eager, graph):
         r.got = {i: [] for i in seqs}
@@ -388,3 +431,54 @@ def test_stop_ids_end_generation_where_the_plain_model_says(models, tmp_path):
     ignored = eng.generate(prompts[:2], SamplingParams(max_tokens=24, ignore_eos=True))
     assert [o.tokens for o in ignored] == free_run[:2] and eng.stats.stop_flag_mismatches == 0
     assert eng.runner.cache.free_pages() == {0: 40}
+
+
+@pytest.mark.parametrize("name", FAST)
+def test_long_decoding_on_the_tma_fed_attention_with_and_without_dependent_launch(models, name):
+    """Decoding at 450 to 640 keys with two key ranges of five 64-key tiles each: the decode
+    attention's TMA thread sends its first tiles before it waits for the kernel that wrote this
+    step's key, which is only right if that kernel (the chain that ends in the rotary encoding
+    and the cache write) is the sole writer of anything those tiles hold.  Run eagerly and from
+    captured graphs, with programmatic dependent launch on and off, three requests side by side
+    (one padding row in the bucket of four); every decoded position against the plain model.
+    The models are sharp, so a key read before it was written moves the logits by tenths."""
+    from rustinfer_b200.engine.runner import ModelRunner, StepEntry
+    from rustinfer_b200.ops import library
+    folder, plain = models[name]
+    V = TINY[name]["vocab_size"]
+    lens, tail = [640, 450, 577], 60
+    seqs = [random_ids(n, V, 900 + i) for i, n in enumerate(lens)]
+    refs = [plain.logits(s) for s in seqs]
+    results = {}
+    try:
+        for pdl in (True, False):
+            library.set_pdl(pdl)
+            for sizes in (None, [1, 2, 4]):
+                r = ModelRunner(folder, dtype="bfloat16", max_model_len=704, page_size=16, num_pages=3 * 44 + 8,
+                                max_batch_seqs=4, max_batch_tokens=1024, capture_sizes=sizes)
+                expect_fast_kernels(r, name)
+                for b in r.model.blocks:
+                    b.mixer.MAX_SPLITS = 2                      # ranges of five tiles: more than the ring holds
+                got = [[] for _ in seqs]
+                for i, s in enumerate(seqs):
+                    r.open(i)
+                    r.step([StepEntry(i, s[: lens[i] - tail], [])])
+                for t in range(tail):
+                    lg = r.step([StepEntry(i, [s[lens[i] - tail + t]], [0]) for i, s in enumerate(seqs)])
+                    for i in range(len(seqs)):
+                        got[i].append(lg[i: i + 1])
+                torch.cuda.synchronize()
+                r.check_kernel_errors()
+                assert (sizes is None) == (r.graph_replays == 0)
+                for i in range(len(seqs)):
+                    out = torch.cat(got[i])
+                    assert rel_err(out, refs[i][lens[i] - tail:]) <= TOL["bfloat16"], (name, pdl, sizes, i)
+                results[(pdl, sizes is not None)] = [torch.cat(g) for g in got]
+    finally:
+        library.set_pdl(True)
+    # the four ways agree with one another far below what a misplaced key would do (they differ
+    # only in the order in which K slices were added into the fp32 stream)
+    base = results[(True, True)]
+    for key, outs in results.items():
+        for a, b in zip(base, outs):
+            assert rel_err(b, a) <= TOL["bfloat16"] / 2, key
