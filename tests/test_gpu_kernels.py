@@ -282,10 +282,11 @@ def test_decode_chain(M, hidden, inter, Hq, Hkv, hd, rot, page):
                 k.ChainProduct(wd_d, m_d, h_d, k.CHAIN_ADD_F32),
                 k.ChainProduct(wqkv_d, h_d, qkv_d, k.CHAIN_ADD_F32, norm=(n2_d, 3e-6), xn=xn_d, rowsq=sq_b)]
     rope = k.ChainRope(qkv_d, pos.to(d), c.float().to(d), s_.float().to(d), slots.to(d), q_d, cache, Hq, Hkv, hd, rot)
-    assert k.decode_chain_fits(products, M, 148)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert k.decode_chain_fits(products, M, sms)
     for _ in range(2):                                       # twice: the barrier and the q,k,v buffer reset themselves
         h_d[:M] = h0.to(d)
-        k.decode_chain(products, rope, M, 148)
+        k.decode_chain(products, rope, M, sms)
     torch.cuda.synchronize()
     assert k.gemm_tc_error(d) == 0
     # ---- the same in float64 from the rounded weights

@@ -613,6 +613,6 @@ def test_toy_parts_of_every_kind_are_registered_built_stepped_and_captured(tmp_p
                 got[i].append(lg[k_: k_ + 1])
                 at[i] += 1
         if sizes is not None:
-            assert r.graph_replays > 50 and 4 in r._graphs
+            assert r.graph_replays > 30 and 4 in r._graphs
         for i in range(3):
             assert rel_err(torch.cat(got[i]), refs[i]) <= tol, (dtype, sizes, i)
