@@ -6,8 +6,14 @@ code with ``rustinfer_b200``: it reads ``config.json`` as a raw dict and the wei
 through the ``safetensors`` package, so a fault in the framework's own configuration
 or loader cannot hide here.
 
-RustInfer's own model code is Rust and no Rust toolchain exists on the build machine,
-so this file could not be compared with a compiled reference: it rests on the formulas.
+RustInfer's own model code is Rust and no Rust toolchain exists on the build machine, so
+the model as a whole could not be run.  Its CUDA kernels could: compiled unmodified and run
+on a B200, their outputs on small inputs lie in tests/golden/reference_kernels.safetensors
+(made by tests/golden/make_reference_goldens.py), and tests/test_reference_goldens.py holds
+the functions of this file to them: rotary tables with llama3 scaling, the rotation,
+RMSNorm alone and fused with the residual add, SwiGLU, and paged grouped-query attention for
+decoding and for prompt portions.  How the parts are put together (decoder_block,
+forward_logits) rests on the formulas.
 Where RustInfer's CPU and CUDA back ends disagree (pairing of RoPE elements, tie-break
 of argmax) the CUDA definition is taken, since that is what serves requests.
 """
