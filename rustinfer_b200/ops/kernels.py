@@ -505,20 +505,26 @@ def decode_feedback(sampled: torch.Tensor, state_slots: torch.Tensor, slot_state
 
 
 def sample(logits: torch.Tensor, scratch: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
-           top_p: torch.Tensor, min_p: torch.Tensor, draw: torch.Tensor, out: torch.Tensor) -> None:
+           top_p: torch.Tensor, min_p: torch.Tensor, draw: torch.Tensor, out: torch.Tensor,
+           by_sorting: bool = False) -> None:
+    """out[r] = the token drawn for row r: logit / temperature, top-k, min-p, top-p, then the token at
+    which the running weight passes draw[r] * (kept weight).  `by_sorting` runs the kernel that sorts
+    every row whole (the slow statement the bucketed kernel falls back to)."""
     require_cuda(logits, scratch, temperature, top_k, top_p, min_p, draw, out)
     R, V = logits.shape
     vpad = 1 << max(1, (V - 1).bit_length())
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits fp32 [R,V]")
-    if scratch.dtype != torch.int64 or scratch.numel() < R * vpad:
-        raise KernelError(f"sample: scratch must hold {R * vpad} int64")
+    if scratch.dtype != torch.int64 or scratch.numel() < R * vpad + R:
+        raise KernelError(f"sample: scratch must hold {R * vpad + R} int64")
     if (temperature.dtype, top_k.dtype, top_p.dtype, min_p.dtype, draw.dtype, out.dtype) != \
             (torch.float32, torch.int32, torch.float32, torch.float32, torch.float64, torch.int32):
         raise KernelError("sample: parameter dtypes")
-    check(L.core().ri_sample(_p(logits), logits.stride(0), R, V, vpad, _p(scratch), _p(temperature),
-                             _p(top_k), _p(top_p), _p(min_p), _p(draw), _p(out), stream_ptr()), "sample")
+    fn = L.core().ri_sample_by_sorting if by_sorting else L.core().ri_sample
+    check(fn(_p(logits), logits.stride(0), R, V, vpad, _p(scratch), _p(temperature),
+             _p(top_k), _p(top_p), _p(min_p), _p(draw), _p(out), stream_ptr()), "sample", 1 if by_sorting else 2)
 
 
 def sample_scratch_elems(rows: int, vocab: int) -> int:
-    return rows * (1 << max(1, (vocab - 1).bit_length()))
+    """int64 words of scratch for `rows` rows: room for the rows that are sorted whole, and a flag a row."""
+    return rows * (1 << max(1, (vocab - 1).bit_length())) + rows

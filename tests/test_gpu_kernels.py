@@ -661,12 +661,17 @@ def test_argmax_lowest_index_wins(V):
     assert out.tolist() == want and out[1] == 7 and out[2] == 0 and out[3] == V - 1
 
 
+@pytest.mark.parametrize("by_sorting", [False, True])
 @pytest.mark.parametrize("V", [130, 391, 5000, 128256])
-def test_sample_matches_the_plain_sampler(V):
+def test_sample_matches_the_plain_sampler(V, by_sorting):
+    """The kernel that finds the filters' boundaries and the drawn token bucket by bucket, and the
+    one that sorts every row whole, against the plain sampler: same tokens.  (The bucketed kernel
+    forms weights in 32-bit and sums them as integers; a row differs from the float64 statement only
+    if a boundary falls within 1e-6 of a running sum, which these seeded rows do not.)"""
     g = torch.Generator().manual_seed(V)
     combos = [(0.8, 0, 1.0, 0.0), (1.0, 5, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
               (0.9, 40, 0.8, 0.01), (0.0, 0, 1.0, 0.0), (1.0, 1, 1.0, 0.0), (1.0, 0, 0.0, 0.0),
-              (2.0, 3, 0.5, 0.2)]
+              (2.0, 3, 0.5, 0.2), (0.5, 1000, 0.95, 0.0), (1.0, 0, 0.3, 0.0)]
     rows = []
     for rep in range(4 if V < 100000 else 2):
         for c in combos:
@@ -674,15 +679,45 @@ def test_sample_matches_the_plain_sampler(V):
     R = len(rows)
     logits = (torch.randn(R, V, generator=g) * 3)
     logits[3, 10] = logits[3, 20] = logits[3].max() + 1          # equal logits: ascending id
+    logits[4, :] = logits[4, :].round() + 0.0                    # many equal logits in every bucket (and no -0.0,
+                                                                 # which the kernels order after +0.0, as a total order does)
+    logits[5, 7] = float("-inf")
+    logits[6, 9] = float("nan")                                  # counts as -inf
+    logits[12, :] = (torch.randn(V, generator=g) * 0.05)         # a flat row: almost every token matters
     draws = torch.rand(R, generator=g, dtype=torch.float64)
+    draws[1], draws[2] = 0.0, 1.0 - 1e-12
     k = K()
     scratch = torch.empty(k.sample_scratch_elems(R, V), dtype=torch.int64, device=dev())
-    out = torch.empty(R, dtype=torch.int32, device=dev())
+    out = torch.full((R,), -7, dtype=torch.int32, device=dev())
     f = lambda i, dt: torch.tensor([r[i] for r in rows], dtype=dt, device=dev())
     k.sample(logits.to(dev()), scratch, f(0, torch.float32), f(1, torch.int32), f(2, torch.float32),
-             f(3, torch.float32), draws.to(dev()), out)
-    want = [P.sample_filtered(logits[i], *rows[i], float(draws[i])) for i in range(R)]
+             f(3, torch.float32), draws.to(dev()), out, by_sorting=by_sorting)
+    clean = torch.nan_to_num(logits, nan=float("-inf"))
+    want = [P.sample_filtered(clean[i], *rows[i], float(draws[i])) for i in range(R)]
     assert out.tolist() == want
+
+
+def test_sample_rows_the_buckets_cannot_take_fall_back_to_the_sort():
+    """All logits equal (one bucket of 20,000 tokens, ordered by id alone), and a row whose maximum is
+    +inf: the bucketed kernel hands them to the sorting kernel, and the tokens are the plain sampler's."""
+    V = 20000
+    g = torch.Generator().manual_seed(3)
+    logits = torch.zeros(4, V)
+    logits[1] = torch.randn(V, generator=g)
+    logits[1, 5] = float("inf")
+    logits[2] = torch.randn(V, generator=g).round() + 0.0        # a few values, thousands of tokens each
+    logits[3] = torch.randn(V, generator=g)
+    draws = torch.tensor([0.37, 0.5, 0.911, 0.2], dtype=torch.float64)
+    k = K()
+    scratch = torch.empty(k.sample_scratch_elems(4, V), dtype=torch.int64, device=dev())
+    out = torch.full((4,), -7, dtype=torch.int32, device=dev())
+    full = lambda v, dt: torch.full((4,), v, dtype=dt, device=dev())
+    k.sample(logits.to(dev()), scratch, full(1.0, torch.float32), full(0, torch.int32), full(1.0, torch.float32),
+             full(0.0, torch.float32), draws.to(dev()), out)
+    assert out[0] == int(0.37 * V)                                # equal weights in id order
+    assert out[1] == 5                                            # the one +inf takes all the weight
+    want = [P.sample_filtered(logits[i], 1.0, 0, 1.0, 0.0, float(draws[i])) for i in (2, 3)]
+    assert out[2:].tolist() == want
 
 
 def test_sample_distribution_and_filters():
