@@ -7,10 +7,17 @@ Llama-3.2-1B-shaped benchmark configuration with random weights ~N(0, 0.02) (see
 batch of 8 and a context that reaches 4,096 tokens.  `value` is decoded tokens a second
 timed on the device over K steps fed with the previous step's tokens on the device; `e2e`
 is the same through `Engine.add_request` / `Engine.step`, host token ids in and out.
-Also reported: a 2,048-token prefill, the decode step against the HBM roofline, decode at
-batch 1 and 64, clocks sampled while timing, and how many of this package's kernels ran.
-`--shape` takes the layer sizes of the 3B or 8B benchmark configuration instead; `--only
-decode|prefill|serve` runs one part alone and prints its time.
+Every timed window is repeated (five times for the headline) and the median is reported with the
+smallest and largest beside it.  Also reported: a 2,048-token prefill, the decode step against the
+HBM roofline, clocks sampled while timing, how many of this package's kernels ran, and under
+`points`: decode and end-to-end decode at batch 1 and 64, decode at batch 8 with temperature
+sampling, the Llama-3.1-8B-shaped model at 8 of its 32 layers (decode at batch 1, 8, 64, a
+2,048-token prefill, one 32,768-token prompt in portions of 8,192 with the share of time spent in
+attention), the Llama-3.2-3B-shaped model at 8 of its 28 layers serving 64 requests at once, and
+this engine's attention and GEMM kernels timed against the reference's own attention kernels
+(compiled unmodified, see baseline/reference_kernels.py) and the library GEMM on the same data.
+`--shape` takes the layer sizes of the 3B or 8B benchmark configuration for the headline instead;
+`--only decode|prefill|serve` runs one part alone and prints its time.
 """
 from __future__ import annotations
 
@@ -136,8 +143,15 @@ def fill_context(engine, batch, ctx0, vocab, seed):
     return ids
 
 
-def decode_device_timed(engine, batch, steps, warmup, vocab, seed, context=CONTEXT):
-    """K decode steps of `batch` requests that end at `context` tokens; device time."""
+def median_of(run, repeats):
+    """`run()` -> (ms, ...): the run whose ms is the median of `repeats` runs, with all the ms."""
+    runs = sorted((run() for _ in range(repeats)), key=lambda r: r[0])
+    return runs[len(runs) // 2], [round(r[0], 4) for r in runs]
+
+
+def decode_device_timed(engine, batch, steps, warmup, vocab, seed, context=CONTEXT, sampling=None):
+    """K decode steps of `batch` requests that end at `context` tokens; device time.  With
+    `sampling` (SamplingParams) every row's token is drawn on the device instead of the argmax."""
     import torch
     from rustinfer_b200.engine.runner import StepEntry
     from rustinfer_b200.ops import library
@@ -147,10 +161,16 @@ def decode_device_timed(engine, batch, steps, warmup, vocab, seed, context=CONTE
     tokens = torch.randint(0, vocab, (batch,), dtype=torch.int32, device=r.device)
     entries = [StepEntry(rid, [0], [0]) for rid in ids]
 
+    at = [ctx0]
+
     def one():
         nonlocal tokens
         logits = r.step(entries, device_tokens=tokens)
-        tokens = engine.sampler.argmax_device(logits)
+        if sampling is None:
+            tokens = engine.sampler.argmax_device(logits)
+        else:
+            at[0] += 1
+            tokens = engine.sampler.sample_device(logits, [sampling] * batch, list(range(batch)), [at[0]] * batch)
 
     r_step = r.step
     r.step = lambda e, device_tokens=None: r_step(e, device_tokens=device_tokens, borrow_logits=True)
@@ -183,6 +203,8 @@ def decode_e2e(engine, batch, steps, warmup, vocab, seed):
     # requests whose prompt is done keep decoding while the others' prompts are computed, so
     # leave room for those extra tokens and end nothing inside the timed region
     ctx0 = CONTEXT - (steps + warmup) - 4 * batch - 8
+    if batch > 8:                                            # prompts of 64 requests take many steps of 8,192 tokens
+        ctx0 = CONTEXT - (steps + warmup) - (batch * CONTEXT) // 8192 - batch - 16
     sp = SamplingParams(max_tokens=CONTEXT, ignore_eos=True)
     for _ in range(batch):
         engine.add_request([rng.randrange(vocab) for _ in range(ctx0)], sp)
@@ -204,6 +226,7 @@ def decode_e2e(engine, batch, steps, warmup, vocab, seed):
     h2d = engine.runner.h2d_bytes_last
     for rid in list(engine._requests):
         engine.abort(rid)
+    torch.cuda.synchronize()
     assert got == batch * (steps - 1), (got, batch, steps)
     return ms, h2d, batch * 8, (w0, w1)       # read back per step: a token id and a stop flag per request
 
@@ -214,7 +237,7 @@ def prefill_timed(engine, vocab, tokens, repeats=3):
     from rustinfer_b200.engine.runner import StepEntry
     r = engine.runner
     rng = random.Random(7)
-    best, windows = None, []
+    times, windows = [], []
     for i in range(repeats + 1):                            # the first run warms up
         rid = ("prefill", i)
         r.open(rid)
@@ -231,15 +254,16 @@ def prefill_timed(engine, vocab, tokens, repeats=3):
         ms = e0.elapsed_time(e1)
         r.close(rid)
         if i > 0:
-            best = ms if best is None else min(best, ms)
-    return best, windows[1:]
+            times.append(ms)
+    return statistics.median(times), windows[1:]
 
 
-def serve_workload(folder, vocab, layers):
+def serve_workload(folder, vocab, layers, quiet=False):
     """Continuous batching through the public entry point: 64 requests arrive at once, prompt
     lengths uniform in [128, 2048], 256 tokens out each, prompts computed in portions of 512
-    beside the decoding of the others.  Prints tokens a second over the whole run (host time:
-    scheduling, launches and the reading of every token included)."""
+    beside the decoding of the others.  Tokens a second over the whole run (host time:
+    scheduling, launches and the reading of every token included), and the time from one
+    step's launch to the next."""
     import random
     import torch
     from rustinfer_b200.engine.engine import Engine
@@ -252,14 +276,182 @@ def serve_workload(folder, vocab, layers):
     engine.generate([p[:64] for p in prompts[:8]], SamplingParams(max_tokens=8, ignore_eos=True))   # warm-up
     torch.cuda.synchronize()
     steps0 = engine.stats.steps
+    ids = [engine.add_request(p, SamplingParams(max_tokens=256, ignore_eos=True)) for p in prompts]
+    marks = []
     t0 = time.perf_counter()
-    results = engine.generate(prompts, SamplingParams(max_tokens=256, ignore_eos=True))
+    while engine.has_unfinished():
+        engine.step()
+        marks.append(time.perf_counter())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    results = [engine.take_finished(i) for i in ids]
+    gaps = sorted((b - a) * 1e3 for a, b in zip(marks, marks[1:]))
     n_in, n_out = sum(len(p) for p in prompts), sum(len(r.tokens) for r in results)
-    print(f"serve layers{layers}: {len(prompts)} requests, {n_in} prompt tokens, {n_out} tokens out in {dt:.3f} s: "
-          f"{n_out / dt:.0f} out tok/s, {(n_in + n_out) / dt:.0f} tok/s in all, {engine.stats.steps - steps0} steps, "
-          f"{engine.stats.preemptions} preemptions")
+    out = {"seconds": round(dt, 4), "out_tok_s": round(n_out / dt, 1), "tok_s": round((n_in + n_out) / dt, 1),
+           "steps": engine.stats.steps - steps0, "preemptions": engine.stats.preemptions,
+           "step_ms_mean": round(sum(gaps) / len(gaps), 4), "step_ms_p99": round(gaps[int(0.99 * (len(gaps) - 1))], 4),
+           "prompt_tokens": n_in, "out_tokens": n_out}
+    if not quiet:
+        print(f"serve layers{layers}: {len(prompts)} requests, {n_in} prompt tokens, {n_out} tokens out in {dt:.3f} s: "
+              f"{n_out / dt:.0f} out tok/s, {(n_in + n_out) / dt:.0f} tok/s in all, {out['steps']} steps "
+              f"(mean {out['step_ms_mean']} ms, p99 {out['step_ms_p99']} ms), {out['preemptions']} preemptions")
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def long_prompt(folder, vocab, cfg, layers, tokens=32768, portion=8192):
+    """One prompt of `tokens` tokens computed in portions through the step function; the time of
+    the attention kernels alone is taken with events around every layer's attention."""
+    import random
+    import torch
+    from rustinfer_b200.engine.engine import Engine
+    from rustinfer_b200.engine.runner import StepEntry
+    from rustinfer_b200.parts.attention import GQAAttention
+    engine = Engine(folder, dtype="bfloat16", max_batch_tokens=portion, max_batch_seqs=1, max_model_len=tokens + 64,
+                    paged_block_size=PAGE, num_blocks=(tokens + 64) // PAGE + 8, capture_sizes=[], ignore_eos=True)
+    r = engine.runner
+    rng = random.Random(5)
+    prompt = [rng.randrange(vocab) for _ in range(tokens)]
+    marks = []
+    plain_attend = GQAAttention.attend
+
+    def timed_attend(self, q, step, cache, out=None):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        res = plain_attend(self, q, step, cache, out)
+        e1.record()
+        marks.append((e0, e1))
+        return res
+
+    best = None
+    for rep in range(2):                                    # the first run warms up
+        r.open(("long", rep))
+        marks.clear()
+        GQAAttention.attend = timed_attend if rep == 1 else plain_attend
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for at in range(0, tokens, portion):
+            n = min(portion, tokens - at)
+            logits = r.step([StepEntry(("long", rep), prompt[at: at + n], [n - 1] if at + n == tokens else [])])
+        engine.sampler.argmax_device(logits)
+        e1.record()
+        torch.cuda.synchronize()
+        best = e0.elapsed_time(e1)
+        r.close(("long", rep))
+    GQAAttention.attend = plain_attend
+    attn_ms = sum(a.elapsed_time(b) for a, b in marks)
+    per_layer, _, _, q_dim = model_numbers(cfg, layers)
+    flops = 2 * tokens * layers * per_layer + 2 * vocab * cfg["hidden_size"] + 2 * tokens * tokens * q_dim * layers
+    del engine
+    torch.cuda.empty_cache()
+    return {"ms": round(best, 2), "tok_s": round(tokens / best * 1e3, 1), "attention_share": round(attn_ms / best, 4),
+            "tflops": round(flops / (best * 1e-3) / 1e12, 1)}
+
+
+def time_kernel(fn, repeats=20, flush=None):
+    """Median device time of fn() in microseconds; `flush` (a large tensor) is rewritten between
+    runs so that nothing of the last run stays in L2."""
+    import torch
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(repeats):
+        if flush is not None:
+            flush.add_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(times)
+
+
+def kernel_ratios():
+    """This engine's attention kernels against the reference's own (compiled unmodified, called
+    through their C launchers with the cache laid out their way), and its tcgen05 GEMM against the
+    library's, on the same data.  reference time / own time: above 1, this engine's kernel is the
+    faster.  The reference's kernels are absent where baseline/_ref was never built: null then."""
+    import math
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_kernels as R
+    from rustinfer_b200.ops import kernels as K
+    dev = torch.device("cuda:0")
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    out = {}
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)           # 256 MB: twice the L2
+    have_ref = R.load() is not None
+    g = torch.Generator(device="cuda").manual_seed(1)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    for tag, (Hq, Hkv, hd) in {"1b": (32, 8, 64), "8b": (32, 8, 128)}.items():
+        scale = 1 / math.sqrt(hd)
+        # ---- decode: 8 requests at 4,096 keys
+        B, ctx = 8, CONTEXT
+        blocks = ctx // PAGE
+        cache = torch.randn(B * blocks, 2, Hkv, PAGE, hd, generator=g, device=dev, dtype=torch.float32).bfloat16()
+        table = torch.randperm(B * blocks, device=dev).to(torch.int32).view(B, blocks).contiguous()
+        q = torch.randn(B, Hq * hd, generator=g, device=dev, dtype=torch.float32).bfloat16()
+        o = torch.empty_like(q)
+        kv_len, cu = i32([ctx] * B), i32(list(range(B + 1)))
+        from rustinfer_b200.parts.base import MIXERS, BuildContext
+        from rustinfer_b200.parts.spec import PartSpec
+        part = MIXERS.build(PartSpec("gqa_attention", {"hidden_size": 64, "num_heads": Hq, "num_kv_heads": Hkv,
+                                                       "head_dim": hd, "scale": scale, "window": None, "position": None}))
+        part.prepare(BuildContext(dev, torch.bfloat16, ctx, PAGE, max_batch_seqs=64, num_sms=sms))
+        splits = part._splits(B, ctx)
+        no, nl = K.decode_scratch_floats(B, Hq, hd, splits)
+        po, pl = torch.empty(no, device=dev), torch.empty(nl, device=dev)
+        own = time_kernel(lambda: K.attention_decode_bf16(q, o, cache, table, cu, kv_len, None, B, Hq, Hkv, hd, scale,
+                                                          None, splits, po, pl), flush=flush)
+        out[f"attn_decode_{tag}_b8_us"] = round(own, 1)
+        if have_ref:
+            kp, vp = R.pools_from_pages(cache, PAGE)
+            ws = R.decode_workspace(B, Hq, hd)
+            o2 = torch.empty_like(q)
+            ref = time_kernel(lambda: R.paged_decode(q, kp, vp, o2, table, kv_len, ws, Hq, Hkv, hd, scale, sms,
+                                                     [ctx] * B), flush=flush)
+            out[f"attn_decode_{tag}_b8_ref_us"] = round(ref, 1)
+            out[f"attn_decode_{tag}_b8_vs_ref"] = round(ref / own, 2)
+            del kp, vp
+        # ---- prompt portion: one request of 2,048 tokens
+        T = PREFILL_TOKENS
+        qp = torch.randn(T, Hq * hd, generator=g, device=dev, dtype=torch.float32).bfloat16()
+        op = torch.empty_like(qp)
+        kvl, cup = i32([T]), i32([0, T])
+        tbl = table[:1, : T // PAGE].contiguous()
+        tc = K.tc_attention_supports(Hq, Hkv, hd, PAGE)
+        tpt = K.tc_tokens_per_tile(Hq, Hkv) if tc else K.mma_tokens_per_tile(Hq, Hkv)
+        te, tq = i32([0] * (T // tpt)), i32(list(range(0, T, tpt)))
+        fn = K.attention_prefill_tc if tc else K.attention_prefill_bf16
+        own = time_kernel(lambda: fn(qp, op, cache, tbl, cup, kvl, te, tq, Hq, Hkv, hd, scale, None), flush=flush)
+        out[f"attn_prefill_{tag}_2048_us"] = round(own, 1)
+        if have_ref:
+            kp, vp = R.pools_from_pages(cache, PAGE)
+            tiles = R.prefill_tiles([T])
+            o2 = torch.empty_like(qp)
+            ref = time_kernel(lambda: R.paged_prefill(qp, kp, vp, o2, tbl, kvl, cup, tiles, [T], [T], Hq, Hkv, hd, scale),
+                              flush=flush)
+            out[f"attn_prefill_{tag}_2048_ref_us"] = round(ref, 1)
+            out[f"attn_prefill_{tag}_2048_vs_ref"] = round(ref / own, 2)
+            del kp, vp
+        del cache
+    # ---- GEMM: the 2,048-token products of the 1B shape against the library's
+    for name, (M, N, Kd) in {"qkv": (2048, 3072, 2048), "gate_up": (2048, 16384, 2048), "down": (2048, 2048, 8192),
+                             "square8192": (8192, 8192, 8192)}.items():
+        x = (torch.randn(M, Kd, generator=g, device=dev) * 0.5).bfloat16()
+        w = (torch.randn(N, Kd, generator=g, device=dev) * 0.02).bfloat16()
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        own = time_kernel(lambda: K.gemm_tc(x, w, y, K.EPI_BF16, num_sms=sms), flush=flush)
+        lib = time_kernel(lambda: torch.mm(x, w.t(), out=y), flush=flush)
+        out[f"gemm_{name}_tflops"] = round(2 * M * N * Kd / own / 1e6, 1)
+        out[f"gemm_{name}_vs_library"] = round(lib / own, 2)
+        del x, w, y
+    del flush
+    torch.cuda.empty_cache()
+    return out
 
 
 def main() -> int:
@@ -272,7 +464,8 @@ def main() -> int:
     ap.add_argument("--shape", default="1b", choices=sorted(SHAPES), help="layer sizes (default: the 1B shape)")
     ap.add_argument("--layers", type=int, default=0,
                     help="fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    ap.add_argument("--skip-points", action="store_true", help="leave out everything under `points`")
+    ap.add_argument("--repeats", type=int, default=5, help="timed windows of the headline (the median is reported)")
     ap.add_argument("--only", choices=["decode", "prefill", "serve"],
                     help="run one part alone and print its time (for profiler captures; no JSON line); "
                          "serve: 64 requests, prompts of 128 to 2,048 tokens, 256 tokens out each, "
@@ -329,30 +522,57 @@ def main() -> int:
                         max_model_len=CONTEXT, paged_block_size=PAGE, chunked_prefill_size=0,
                         num_blocks=64 * CONTEXT // PAGE + 64, capture_sizes=[1, 2, 4, 8, 16, 32, 64],
                         ignore_eos=True)
-        ms_step, launches, w = decode_device_timed(engine, args.batch, args.steps, args.warmup, vocab, 1)
+        say = lambda msg: print(f"[bench] {msg}", file=sys.stderr, flush=True)
+        reps = args.repeats
+        seeds = iter(range(100, 10_000))
+        # ---- the headline: K decode steps at the asked batch, device-timed, repeated
+        (ms_step, launches, w), decode_ms = median_of(
+            lambda: decode_device_timed(engine, args.batch, args.steps, args.warmup, vocab, next(seeds)), reps)
         windows.append(w)
-        print(f"[bench] decode b{args.batch}: {ms_step:.4f} ms/step", file=sys.stderr, flush=True)
-        e2e_ms, h2d, d2h, w = decode_e2e(engine, args.batch, args.steps, args.warmup, vocab, 2)
+        say(f"decode b{args.batch}: {ms_step:.4f} ms/step (of {decode_ms})")
+        (e2e_ms, h2d, d2h, w), e2e_all = median_of(
+            lambda: decode_e2e(engine, args.batch, args.steps, args.warmup, vocab, next(seeds)), reps)
         windows.append(w)
-        print(f"[bench] e2e b{args.batch}: {e2e_ms:.4f} ms/step", file=sys.stderr, flush=True)
-        prefill_ms, pw = prefill_timed(engine, vocab, PREFILL_TOKENS)
+        say(f"e2e b{args.batch}: {e2e_ms:.4f} ms/step (of {e2e_all})")
+        prefill_ms, pw = prefill_timed(engine, vocab, PREFILL_TOKENS, repeats=reps)
         windows += pw
-        print(f"[bench] prefill {PREFILL_TOKENS}: {prefill_ms:.3f} ms", file=sys.stderr, flush=True)
+        say(f"prefill {PREFILL_TOKENS}: {prefill_ms:.3f} ms")
         points = {}
         if not args.skip_points:
+            from rustinfer_b200.sampling.params import SamplingParams
+            k = min(args.steps, 64)
             for b in (1, 64):
-                k = min(args.steps, 64)
-                ms_b, _, w = decode_device_timed(engine, b, k, args.warmup, vocab, 10 + b)
+                (ms_b, _, w), _all = median_of(lambda: decode_device_timed(engine, b, k, args.warmup, vocab, next(seeds)), 3)
                 windows.append(w)
                 points[f"decode_b{b}"] = round(b / ms_b * 1e3, 1)
+                points[f"decode_b{b}_hbm_frac"] = round(step_bytes_of(cfg, args.layers, b, CONTEXT - k / 2) / (ms_b * 1e-3) / 1e9 / hbm_gbs, 4)
+                (ms_e, _, _, w), _all = median_of(lambda: decode_e2e(engine, b, k, args.warmup, vocab, next(seeds)), 3)
+                windows.append(w)
+                points[f"e2e_b{b}"] = round(b / ms_e * 1e3, 1)
+                say(f"decode b{b}: {ms_b:.4f} ms/step, e2e {ms_e:.4f}")
+            # the same steps with every token drawn (temperature 0.8, top-k 50, top-p 0.9) instead of the argmax
+            sp = SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=1, max_tokens=CONTEXT, ignore_eos=True)
+            (ms_s, _, w), _all = median_of(
+                lambda: decode_device_timed(engine, args.batch, k, args.warmup, vocab, next(seeds), sampling=sp), 3)
+            windows.append(w)
+            points[f"decode_b{args.batch}_sampled"] = round(args.batch / ms_s * 1e3, 1)
+            say(f"decode b{args.batch} sampled: {ms_s:.4f} ms/step")
+        del engine
+        torch.cuda.empty_cache()
+    if not args.skip_points and args.shape == "1b":
+        points.update(further_shapes(args, hbm_gbs, bf16_tflops, windows, say))
+        try:
+            points.update(kernel_ratios())
+        except Exception as e:                                # the comparison must not cost the headline its line
+            points["kernel_ratios_error"] = f"{type(e).__name__}: {e}"[:200]
     clocks.stop()
 
     value = args.batch / ms_step * 1e3
     mean_ctx = CONTEXT - args.steps / 2
-    step_bytes = weight_bytes + args.batch * mean_ctx * kv_per_token
+    step_bytes = step_bytes_of(cfg, args.layers, args.batch, mean_ctx)
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
     T = PREFILL_TOKENS
-    prefill_flops = 2 * T * args.layers * per_layer + 2 * vocab * cfg["hidden_size"] + 2 * T * T * q_dim * args.layers
+    prefill_flops = prefill_flops_of(cfg, args.layers, T)
     prefill_frac = prefill_flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12)
     out = {
         "metric": f"decode tok/s @ batch {args.batch}, context {CONTEXT} ({shape_name}, bf16, random weights)",
@@ -366,7 +586,8 @@ def main() -> int:
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "tied_head": cfg["tie_word_embeddings"],
                    "page_size": PAGE, "prefill_tokens": T, "cuda_graphs": True,
                    "l2": "each step reads %.2f GB of weights and cache, far beyond the 126 MB L2" % (step_bytes / 1e9),
-                   "peaks": peak_kind},
+                   "peaks": peak_kind, "windows": f"median of {reps} windows of {args.steps} steps"},
+        "spread": {"decode_ms": decode_ms, "e2e_ms": e2e_all},
         "e2e": {"value": round(args.batch / e2e_ms * 1e3, 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4)},
         "gpu_launches": launches,
@@ -379,6 +600,77 @@ def main() -> int:
     }
     print(json.dumps(out))
     return 0
+
+
+def step_bytes_of(cfg, layers, batch, mean_ctx):
+    """Bytes a decode step has to read: every weight once, and the cache of the live requests."""
+    _, weight_bytes, kv_per_token, _ = model_numbers(cfg, layers)
+    if not cfg["tie_word_embeddings"]:
+        weight_bytes += 0                                    # the untied head is the table counted; the embedding is only gathered
+    return weight_bytes + batch * mean_ctx * kv_per_token
+
+
+def prefill_flops_of(cfg, layers, T):
+    per_layer, _, _, q_dim = model_numbers(cfg, layers)
+    return 2 * T * layers * per_layer + 2 * cfg["vocab_size"] * cfg["hidden_size"] + 2 * T * T * q_dim * layers
+
+
+def further_shapes(args, hbm_gbs, bf16_tflops, windows, say):
+    """The other benchmark configurations, at 8 of their layers each (both numbers are in the
+    keys): the 8B shape (decode at batch 1, 8, 64, a 2,048-token prefill, one 32,768-token prompt)
+    and the 3B shape serving 64 requests at once."""
+    import torch
+    from rustinfer_b200.engine.engine import Engine
+    from rustinfer_b200.weights.random_init import write_random_model
+    out = {}
+    seeds = iter(range(20_000, 30_000))
+    k = min(args.steps, 32)
+    # ---- Llama-3.1-8B-shaped, 8 of 32 layers
+    name, shape = SHAPES["8b"]
+    layers = 8
+    cfg = dict(shape, num_hidden_layers=layers)
+    tag = f"8b_l{layers}of{shape['num_hidden_layers']}"
+    with tempfile.TemporaryDirectory(prefix="rustinfer_b200_bench_") as tmp:
+        folder = write_random_model(os.path.join(tmp, "model"), cfg, seed=4, std=STD)
+        engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=64, max_model_len=CONTEXT,
+                        paged_block_size=PAGE, num_blocks=64 * CONTEXT // PAGE + 64,
+                        capture_sizes=[1, 2, 4, 8, 16, 32, 64], ignore_eos=True)
+        for b in (1, 8, 64):
+            (ms_b, _, w), _all = median_of(lambda: decode_device_timed(engine, b, k, args.warmup, cfg["vocab_size"], next(seeds)), 3)
+            windows.append(w)
+            out[f"{tag}_decode_b{b}"] = round(b / ms_b * 1e3, 1)
+            out[f"{tag}_decode_b{b}_hbm_frac"] = round(step_bytes_of(cfg, layers, b, CONTEXT - k / 2) / (ms_b * 1e-3) / 1e9 / hbm_gbs, 4)
+            say(f"{tag} decode b{b}: {ms_b:.4f} ms/step")
+        ms_p, pw = prefill_timed(engine, cfg["vocab_size"], PREFILL_TOKENS, repeats=3)
+        windows += pw
+        out[f"{tag}_prefill_2048"] = round(PREFILL_TOKENS / ms_p * 1e3, 1)
+        out[f"{tag}_prefill_2048_tc_frac"] = round(prefill_flops_of(cfg, layers, PREFILL_TOKENS) / (ms_p * 1e-3) / (bf16_tflops * 1e12), 4)
+        say(f"{tag} prefill 2048: {ms_p:.3f} ms")
+        del engine
+        torch.cuda.empty_cache()
+        w0 = time.time()
+        lp = long_prompt(folder, cfg["vocab_size"], cfg, layers)
+        windows.append((w0, time.time()))
+        out[f"{tag}_prompt_32768"] = lp["tok_s"]
+        out[f"{tag}_prompt_32768_attention_share"] = lp["attention_share"]
+        out[f"{tag}_prompt_32768_tc_frac"] = round(lp["tflops"] / bf16_tflops, 4)
+        say(f"{tag} prompt of 32,768: {lp['ms']} ms, attention {lp['attention_share']:.0%}")
+    # ---- Llama-3.2-3B-shaped, 8 of 28 layers: 64 requests at once through Engine
+    name, shape = SHAPES["3b"]
+    cfg = dict(shape, num_hidden_layers=layers)
+    tag = f"3b_l{layers}of{shape['num_hidden_layers']}"
+    with tempfile.TemporaryDirectory(prefix="rustinfer_b200_bench_") as tmp:
+        folder = write_random_model(os.path.join(tmp, "model"), cfg, seed=3, std=STD)
+        w0 = time.time()
+        sv = serve_workload(folder, cfg["vocab_size"], layers, quiet=True)
+        windows.append((w0, time.time()))
+        out[f"{tag}_serve64_tok_s"] = sv["tok_s"]
+        out[f"{tag}_serve64_out_tok_s"] = sv["out_tok_s"]
+        out[f"{tag}_serve64_step_ms_mean"] = sv["step_ms_mean"]
+        out[f"{tag}_serve64_step_ms_p99"] = sv["step_ms_p99"]
+        out[f"{tag}_serve64_preemptions"] = sv["preemptions"]
+        say(f"{tag} serve: {sv}")
+    return out
 
 
 if __name__ == "__main__":
