@@ -919,12 +919,14 @@ RI_API int ri_attention_prefill_bf16(const void* q, int q_stride, void* out, int
 }
 
 // Scratch for `splits` > 1: part_o holds entries*Hq*splits*HD floats, part_lse entries*Hq*splits.
+// With `merge` 0 and several key ranges the partial results are left there for the caller to merge
+// (the chained products do it while they lay out their first operand) and `out` is not written.
 RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int out_stride,
                                     const void* cache, const int* block_table, int table_stride,
                                     const int* cu_q, const int* kv_len, const int* entry_list,
                                     int n_entries, int Hq, int Hkv, int page_size, float scale, int window,
                                     int splits, float* part_o, float* part_lse, long long n_pages, int* error,
-                                    void* stream) {
+                                    int merge, void* stream) {
     if (n_entries <= 0) return 0;
     if (Hkv <= 0 || Hq % Hkv != 0 || splits < 1 || (splits > 1 && (!part_o || !part_lse)))
         return (int)cudaErrorInvalidValue;
@@ -944,7 +946,7 @@ RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int 
             (const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_stride, cu_q, kv_len, entry_list,
             Hq, Hkv, Gc, chunks, page_size, box_rows, scale * 1.4426950408889634f, window, splits, part_o, part_lse, error));
         st = ri_launch_status();
-        if (st != 0 || splits == 1) return st;
+        if (st != 0 || splits == 1 || !merge) return st;
         RI_CHECKED(ri_launch(combine_kernel, dim3(dim3(n_entries, Hq)), dim3(HD < 128 ? 64 : 128), 0, s,
             part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits));
         return ri_launch_status();
@@ -955,7 +957,7 @@ RI_API int ri_attention_decode_bf16(const void* q, int q_stride, void* out, int 
         cu_q, kv_len, entry_list, Hq, Hkv, Gc, chunks, page_size, scale * 1.4426950408889634f, window,
         splits, part_o, part_lse));
     st = ri_launch_status();
-    if (st != 0 || splits == 1) return st;
+    if (st != 0 || splits == 1 || !merge) return st;
     RI_CHECKED(ri_launch(combine_kernel, dim3(dim3(n_entries, Hq)), dim3(HD < 128 ? 64 : 128), 0, s, 
         part_o, part_lse, (bf16*)out, out_stride, cu_q, entry_list, Hq, splits));
     return ri_launch_status();

@@ -41,7 +41,7 @@ constexpr int HEAD_BYTES = 1024;               // barriers and row scales in fro
 constexpr int ROW_STAGE_BYTES = 64 * 1024;     // most bytes of fp32 stream rows staged at a time
 constexpr int SMEM_LIMIT = 225 * 1024;
 
-enum XKind { X_BF16 = 0, X_NORM = 1 };
+enum XKind { X_BF16 = 0, X_NORM = 1, X_PARTIALS = 2 };
 enum OutKind { OUT_ADD_F32 = 0, OUT_SILU_BF16 = 1, OUT_BF16 = 2 };
 enum ErrorCode { ERR_CHAIN_PRODUCER = 11, ERR_CHAIN_MMA = 12, ERR_CHAIN_EPILOGUE = 13, ERR_CHAIN_GRID = 14 };
 
@@ -49,7 +49,9 @@ struct Phase {
     int N, K;                   // weight [N][K]
     int a_box, tiles, splits, per;   // weight rows per tile, tiles along N, K slices, stages (KSTEP columns) per slice
     int x_kind, ld_x;
-    const void* x;              // X_BF16: bf16 [M][ld_x];  X_NORM: fp32 [M][ld_x]
+    const void* x;              // X_BF16: bf16 [M][ld_x];  X_NORM: fp32 [M][ld_x];  X_PARTIALS: fp32 partial attention outputs
+    const float* part_lse;      // X_PARTIALS: log-sum-exps of the key ranges
+    int part_splits, part_heads, part_hd;
     const void* norm_w;         // X_NORM: [K]
     int norm_w_bf16;
     float eps;
@@ -263,6 +265,42 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                     }
                     ok = mbar_wait(x_land, xl & 1, p.error, ERR_CHAIN_EPILOGUE);
                     ++xl;
+                } else if (P.x_kind == X_PARTIALS) {
+                    // the attention before this chain left one partial output per key range: the
+                    // operand's element (token r, head h, dim d) is their merge,
+                    // sum_s 2^(lse_s - max) part_s / sum_s 2^(lse_s - max), formed here instead of
+                    // by a kernel of its own (16 bytes of the operand a thread and turn)
+                    const float* po = reinterpret_cast<const float*>(P.x);
+                    const float* pl = P.part_lse;
+                    const int S = P.part_splits, hd = P.part_hd, Hq = P.part_heads, Kc = P.K, x_kb_bytes = p.x_kb_bytes;
+                    const int cpr = n_kb * (BK >> 3);                       // 16-byte chunks of a row in this K slice
+                    for (int idx = te; idx < M * cpr; idx += 128) {
+                        const int r = idx / cpr, c = idx - r * cpr;
+                        const int k = kb0 * BK + c * 8;
+                        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                        if (k < Kc) {
+                            const int h = k / hd, d = k - h * hd;
+                            const size_t at = ((size_t)r * Hq + h) * S;
+                            float mx = -INFINITY;
+                            for (int s = 0; s < S; ++s) mx = fmaxf(mx, pl[at + s]);
+                            float W = 0.f;
+                            if (mx != -INFINITY) {
+                                for (int s = 0; s < S; ++s) {
+                                    const float w = exp2f(pl[at + s] - mx);
+                                    const float4 a = *reinterpret_cast<const float4*>(po + (at + s) * hd + d);
+                                    const float4 b = *reinterpret_cast<const float4*>(po + (at + s) * hd + d + 4);
+                                    W += w;
+                                    acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
+                                    acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
+                                }
+                            }
+                            const float inv = W > 0.f ? 1.f / W : 0.f;
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[e] *= inv;
+                        }
+                        *reinterpret_cast<uint4*>(xs + (size_t)(c >> 3) * x_kb_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = pack8(acc);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 } else {
                     // rows of the fp32 stream are staged whole: the sum of squares needs all of a
                     // row, the operand only this slice of it, times the norm weight (the RMS scale
@@ -582,7 +620,10 @@ RI_API int ri_decode_chain(const RiChainPhase* phases, int n_phases, const RiCha
         const RiChainPhase& f = phases[i];
         Phase& P = p.ph[i];
         if (!f.w || !f.x || !f.out || (reinterpret_cast<uintptr_t>(f.w) & 15) || (reinterpret_cast<uintptr_t>(f.x) & 15) ||
-            f.out_kind < 0 || f.out_kind > 2 || f.x_kind < 0 || f.x_kind > 1)
+            f.out_kind < 0 || f.out_kind > 2 || f.x_kind < 0 || f.x_kind > 2)
+            return (int)cudaErrorInvalidValue;
+        if (f.x_kind == X_PARTIALS && (!f.part_lse || f.part_splits < 1 || f.part_head_dim < 8 || f.part_head_dim % 8 ||
+                                       f.part_heads * f.part_head_dim != f.K))
             return (int)cudaErrorInvalidValue;
         if (f.x_kind == X_BF16 && (f.ld_x % 8 || f.x_rows < (M <= 8 ? 8 : L.bn))) return (int)cudaErrorInvalidValue;
         if (f.x_kind == X_NORM && (f.ld_x % 4 || !f.norm_w || (reinterpret_cast<uintptr_t>(f.norm_w) & 15))) return (int)cudaErrorInvalidValue;
@@ -590,6 +631,7 @@ RI_API int ri_decode_chain(const RiChainPhase* phases, int n_phases, const RiCha
         P.N = f.N; P.K = f.K;
         plan_phase(f, sms, &P.a_box, &P.tiles, &P.splits, &P.per);
         P.x_kind = f.x_kind; P.ld_x = f.ld_x; P.x = f.x; P.norm_w = f.norm_w;
+        P.part_lse = f.part_lse; P.part_splits = f.part_splits; P.part_heads = f.part_heads; P.part_hd = f.part_head_dim;
         P.norm_w_bf16 = f.norm_w_dtype == RI_BF16 ? 1 : 0; P.eps = f.eps;
         P.out_kind = f.out_kind; P.ld_out = f.ld_out; P.out = f.out;
         RI_CHECKED(ri_tc_weight_map(f.w, f.N, f.K, P.a_box, &maps.m[i]));

@@ -8,7 +8,7 @@ struct RiChainPhase {
     const void* w;              // bf16 [N][K], K a multiple of 8, 16-byte aligned
     int N, K;
     int x_kind;                 // 0: x is bf16 [M][ld_x]; 1: x is the fp32 stream [M][ld_x] and the
-    int ld_x;                   //    operand is x * norm_w * rsqrt(mean(x^2) + eps)
+    int ld_x;                   //    operand is x * norm_w * rsqrt(mean(x^2) + eps); 2: see `part_o`
     int x_rows;                 // rows the matrix x really has (a TMA box reads 8, 16 or 32 of them)
     const void* x;
     const void* norm_w;
@@ -21,6 +21,13 @@ struct RiChainPhase {
     // [64][K], unscaled) and for the rows' sums of squares (64 floats, zero between launches)
     void* xn;
     float* rowsq;
+    // x_kind 2 (steps of up to 16 tokens): the operand is the attention output of M single-token
+    // entries whose key ranges have not been merged yet; x points at the partial outputs, fp32
+    // [M][part_heads][part_splits][part_head_dim] (K = part_heads * part_head_dim), part_lse at
+    // their base-2 log-sum-exps [M][part_heads][part_splits]; the merge happens while the operand
+    // is laid out in shared memory
+    const float* part_lse;
+    int part_splits, part_heads, part_head_dim;
 };
 
 struct RiChainRope {

@@ -488,6 +488,7 @@ int ri_decode_chain_wide_fits(const RiChainPhase* phases, int n_phases, int M, i
     for (int i = 0; i < n_phases; ++i) {
         Phase P;
         if (!plan_product(phases[i], sms, &P)) return 0;
+        if (phases[i].x_kind == 2) return 0;               // unmerged key ranges: the chain for up to 16 tokens alone takes them
         if (phases[i].x_kind == 1 && (!phases[i].xn || !phases[i].rowsq)) return 0;
         total += phases[i].x_kind == 1 ? 2 : 1;
     }

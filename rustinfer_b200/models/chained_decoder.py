@@ -39,6 +39,7 @@ class ChainedDecoder:
         self.d = decoder
         self.ctx = decoder.ctx
         self.max_tokens = max_tokens
+        self.fold_merge = os.environ.get("RUSTINFER_B200_FOLD_MERGE", "1") != "0"
         self.entries = [(decoder.blocks[e.layer], i) for i, e in enumerate(decoder.spec.run_order)]
         # Everything small that the chains touch (stream, activations, norm weights) lies in one
         # arena that starts on a 2 MB boundary: while gigabytes of weights stream past, these
@@ -141,7 +142,11 @@ class ChainedDecoder:
             attn = self._buffer("attn", a.Hq * a.hd, torch.bfloat16)
             mid = self._buffer("mid", f.inter, torch.bfloat16)
             rows = K.CHAIN_MAX_TOKENS
-            products = [K.ChainProduct(a.o.weight, attn[:T], self.h[:T], K.CHAIN_ADD_F32, x_rows=rows),
+            # up to 16 single tokens whose keys were cut into ranges: the output product merges the
+            # ranges itself while it lays out its operand, and the attention launches no merge
+            ranges = a.unmerged_ranges(step) if (step is not None and T <= 16 and self.fold_merge) else 0
+            partials = (a.part_o, a.part_lse, ranges, a.Hq, a.hd) if ranges else None
+            products = [K.ChainProduct(a.o.weight, attn[:T], self.h[:T], K.CHAIN_ADD_F32, x_rows=rows, partials=partials),
                         K.ChainProduct(f.gate_up.weight, self.h[:T], mid[:T], K.CHAIN_SILU_BF16,
                                        norm=(self.norm_w[id(block.ffn_norm)], block.ffn_norm.eps),
                                        xn=self._buffer("xn", a.hidden, torch.bfloat16),
@@ -169,7 +174,7 @@ class ChainedDecoder:
             a = block.mixer
             q = self._buffer("q", a.Hq * a.hd, torch.bfloat16)[:T]
             attn = self._buffer("attn", a.Hq * a.hd, torch.bfloat16)
-            a.attend(q, step, caches[i], out=attn[:T])
+            a.attend(q, step, caches[i], out=attn[:T], merge=chains[i + 1][0][0].partials is None)
             K.decode_chain(chains[i + 1][0], chains[i + 1][1], T, sms)
         if logit_rows is None or logit_rows.numel() == 0:
             return None

@@ -216,7 +216,8 @@ class _ChainPhase(ctypes.Structure):
                 ("ld_x", ctypes.c_int), ("x_rows", ctypes.c_int), ("x", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),
                 ("norm_w_dtype", ctypes.c_int), ("eps", ctypes.c_float), ("out_kind", ctypes.c_int),
                 ("ld_out", ctypes.c_int), ("out", ctypes.c_void_p), ("xn", ctypes.c_void_p),
-                ("rowsq", ctypes.c_void_p)]
+                ("rowsq", ctypes.c_void_p), ("part_lse", ctypes.c_void_p), ("part_splits", ctypes.c_int),
+                ("part_heads", ctypes.c_int), ("part_head_dim", ctypes.c_int)]
 
 
 class _ChainRope(ctypes.Structure):
@@ -240,8 +241,18 @@ class ChainProduct:
 
     def __init__(self, w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, out_kind: int, norm=None,
                  x_rows: Optional[int] = None, xn: Optional[torch.Tensor] = None,
-                 rowsq: Optional[torch.Tensor] = None):
+                 rowsq: Optional[torch.Tensor] = None, partials=None):
         self.w, self.x, self.out, self.out_kind, self.norm = w, x, out, out_kind, norm
+        # partials = (part_o, part_lse, splits, heads, head_dim): instead of reading `x`, the product
+        # merges the key ranges a split decode attention left (steps of up to 16 tokens, one token an entry)
+        self.partials = partials
+        if partials is not None:
+            po, pl, splits, heads, hd = partials
+            M = x.shape[0]
+            if (norm is not None or po.dtype != torch.float32 or pl.dtype != torch.float32 or heads * hd != w.shape[1]
+                    or hd % 8 or po.numel() < M * heads * splits * hd or pl.numel() < M * heads * splits
+                    or po.data_ptr() % 16 or M > 16):
+                raise KernelError("decode_chain: the partial attention results do not fit this product")
         # steps of more than 16 tokens with a norm: room for the normed operand, bf16 [64, K], and
         # for the rows' sums of squares, fp32 [64], zero before the first use (the kernel leaves it zero)
         self.xn, self.rowsq = xn, rowsq
@@ -272,6 +283,12 @@ class ChainProduct:
         c.out, c.ld_out, c.out_kind = self.out.data_ptr(), self.out.stride(0), self.out_kind
         c.xn = self.xn.data_ptr() if self.xn is not None else None
         c.rowsq = self.rowsq.data_ptr() if self.rowsq is not None else None
+        if self.partials is not None:
+            po, pl, splits, heads, hd = self.partials
+            c.x_kind, c.x, c.part_lse = 2, po.data_ptr(), pl.data_ptr()
+            c.part_splits, c.part_heads, c.part_head_dim = int(splits), int(heads), int(hd)
+        else:
+            c.part_lse, c.part_splits, c.part_heads, c.part_head_dim = None, 0, 0, 0
 
 
 class ChainRope:
@@ -435,11 +452,13 @@ def decode_scratch_floats(entries: int, num_heads: int, head_dim: int, splits: i
 def attention_decode_bf16(q, out, cache, block_table, cu_q, kv_len, entry_list: Optional[torch.Tensor],
                           n_entries: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                           window: Optional[int], splits: int, part_o: Optional[torch.Tensor],
-                          part_lse: Optional[torch.Tensor], by_tma: bool = True) -> None:
+                          part_lse: Optional[torch.Tensor], by_tma: bool = True, merge: bool = True) -> None:
     """Entries of one token each (entry_list: their indices, None = 0..n-1); `splits` > 1
     cuts each entry's keys into that many ranges whose partial results go through
     part_o / part_lse (fp32 scratch).  Head sizes 64 and 128 with pages of 8, 16, 32 or a
-    multiple of 64 keys fetch keys and values by TMA unless `by_tma` is False."""
+    multiple of 64 keys fetch keys and values by TMA unless `by_tma` is False.  With `merge`
+    False (and several ranges) the ranges are not merged: `out` stays unwritten and the caller
+    reads part_o [entries, Hq, splits, hd] and part_lse [entries, Hq, splits] itself."""
     _attention_args(q, out, cache, block_table, cu_q, kv_len, num_heads, num_kv_heads, head_dim)
     require_cuda(entry_list, part_o, part_lse)
     _i32(entry_list, "entry_list")
@@ -454,7 +473,8 @@ def attention_decode_bf16(q, out, cache, block_table, cu_q, kv_len, entry_list: 
                                        num_heads, num_kv_heads, cache.shape[3], float(scale),
                                        int(window) if window else 0, int(splits), _p(part_o), _p(part_lse),
                                        cache.shape[0] if by_tma else 0, _p(gemm_tc_state(q.device)[2]),
-                                       stream_ptr()), "attention_decode_bf16", 2 if splits > 1 else 1)
+                                       1 if merge else 0, stream_ptr()), "attention_decode_bf16",
+          2 if splits > 1 and merge else 1)
 
 
 _argmax_state = {}

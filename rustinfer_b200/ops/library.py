@@ -30,7 +30,7 @@ _SIGNATURES = {
     "ri_sample": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "ri_sample_by_sorting": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _P],
     "ri_attention_prefill_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-    "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _L, _P, _P],
+    "ri_attention_decode_bf16": [_P, _I, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P, _L, _P, _I, _P],
     "ri_attention_mma_tokens_per_tile": [_I],
     "ri_attention_prefill_tc": [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "ri_attention_tc_supports": [_I, _I, _I],

@@ -131,10 +131,21 @@ class GQAAttention(Mixer):
                            self.hd, 0)
         return self._project_out(self.attend(qkv[:, : self.Hq * self.hd], step, cache), residual)
 
+    def unmerged_ranges(self, step: StepContext) -> int:
+        """Key ranges a step of single tokens only is cut into when its caller merges them itself
+        (`attend(..., merge=False)`); 0 when there is nothing to merge (another kind of step, one
+        range, or the kernel without ranges)."""
+        if not self.use_mma or not step.decode_only:
+            return 0
+        splits = self._splits(step.num_tokens, step.max_kv_len)
+        return splits if splits > 1 else 0
+
     def attend(self, q: torch.Tensor, step: StepContext, cache: PagedLayerCache,
-               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, merge: bool = True) -> torch.Tensor:
         """Attention of the rotated queries q [T, Hq*hd] (unit column stride) over the cache, whose
-        pages already hold this step's keys and values: [T, Hq*hd] (into `out` if given)."""
+        pages already hold this step's keys and values: [T, Hq*hd] (into `out` if given).  With
+        `merge` False in a step for which `unmerged_ranges` is not 0, the key ranges' partial
+        results stay in `self.part_o` / `self.part_lse` and `out` is not written."""
         T = step.num_tokens
         g = step.groups[cache.group]
         if out is None:
@@ -149,7 +160,8 @@ class GQAAttention(Mixer):
             splits = self._splits(single.numel(), step.max_kv_len)
             K.attention_decode_bf16(q, out, cache.kv, g.block_table, step.cu_q, step.kv_len,
                                     single, single.numel(), self.Hq, self.Hkv, self.hd,
-                                    self.scale, self.window, splits, self.part_o, self.part_lse)
+                                    self.scale, self.window, splits, self.part_o, self.part_lse,
+                                    merge=merge or not step.decode_only)
         tile_entry, tile_tok0 = step.index(self._tiles)
         if tile_entry.numel():
             prefill = K.attention_prefill_tc if self.use_tc else K.attention_prefill_bf16
