@@ -179,56 +179,57 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap cache_map, const Params 
     const unsigned tmem_base = *tmem_slot;
     pdl_trigger();
 
-    if (warp == 0 && lane == 0) {
+    if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        // The whole warp: lane 0 waits for a free stage and announces the bytes, then every box
+        // of the tile goes out from a lane of its own.  A box is one page's keys (or values) of
+        // one 64-column block, 2 KB with pages of 16; one thread sends a box every 74 ns, and 8 to
+        // 16 boxes a tile from one thread were the period of the whole kernel (1.2 to 2.4 us a
+        // tile against 0.2 to 0.4 us of tensor-core work).
         pdl_wait();                                            // the cache was written by the kernel before
         const int* bt = p.block_table + (size_t)b * p.table_stride;
         const int boxes = BN / p.box_rows;                     // at most 8 pages meet a tile
         bool ok = true;
-        // This one thread sets the pace of the CTA, so it does no division and waits for no
-        // look-up: pages are smaller than a tile (a box per page, from its first key) or whole
-        // multiples of it (one box, block and offset counted along), and the page numbers of
-        // a tile are read from the block table one tile ahead, all at once.  (Eight look-ups
-        // and sixteen divisions in a row before the boxes of a tile went out took 1.5 us and
-        // were the period of the whole kernel.)
-        // Pages past the request's last one are never allocated: its first page is read instead
-        // (those keys are masked, and their V rows are zeroed before use).
+        // Pages are smaller than a tile (a box per page, from its first key) or whole multiples
+        // of it (one box, block and offset counted along).  Pages past the request's last one
+        // are never allocated: its first page is read instead (those keys are masked, and their
+        // V rows are zeroed before use).
         const bool small_pages = p.page_size < BN;
         int blk = (t_begin * BN) / p.page_size, off = small_pages ? 0 : (t_begin * BN) % p.page_size;
-        int pages[8], pages_next[8];
-        auto look_up = [&](int key0, int blk0, bool live, int (&out)[8]) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                out[c] = (live && c < boxes) ? bt[key0 + c * p.box_rows < kvl ? blk0 + c : 0] : 0;
-        };
-        look_up(t_begin * BN, blk, n_tiles > 0, pages);
         const int kv_step = p.Hkv * p.page_size;               // rows between a page's keys and its values
+        // this lane's box of a tile: page c of the tile, 64-column block kb.  The page number of the
+        // next tile's box is read one tile ahead, so that no box waits for a look-up.
+        const int c = lane / KB, kb = lane - c * KB;
+        const bool mine = c < boxes;
+        auto page_of = [&](int key0, int blk0) -> int {
+            if (!mine) return 0;
+            const bool live = key0 + c * p.box_rows < kvl;
+            return bt[live ? blk0 + (small_pages ? c : 0) : 0];
+        };
+        int page = n_tiles > 0 ? page_of(t_begin * BN, blk) : 0;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int s = j % NS, u = j / NS;
             const int key0 = (t_begin + j) * BN;
             int blk_n = blk, off_n = off;
             if (small_pages) blk_n += boxes;
             else if ((off_n += BN) >= p.page_size) { off_n = 0; ++blk_n; }
-            look_up(key0 + BN, blk_n, j + 1 < n_tiles, pages_next);
+            const int page_next = j + 1 < n_tiles ? page_of(key0 + BN, blk_n) : 0;
+            const int row = (page * 2 * p.Hkv + g) * p.page_size + (key0 + c * p.box_rows < kvl ? off : 0);
             for (int kv = 0; kv < 2 && ok; ++kv) {
                 uint64_t* full = kv ? &v_full[s] : &k_full[s];
                 uint64_t* empty = kv ? &v_empty[s] : &k_empty[s];
-                if (u > 0 && !mbar_wait(empty, (u - 1) & 1, p.error, ERR_PRODUCER)) { ok = false; break; }
-                unsigned char* dst = sm + (kv ? OFF_V : OFF_K) + s * KV_STAGE;
-                mbar_expect_tx(full, KV_STAGE);
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    if (c < boxes) {
-                        const int row = (pages[c] * 2 * p.Hkv + g) * p.page_size + kv * kv_step +
-                                        (key0 + c * p.box_rows < kvl ? off : 0);
-                        for (int kb = 0; kb < KB; ++kb)
-                            tma_load_2d(dst + kb * (BN * 128) + c * p.box_rows * 128, &cache_map, full, kb * 64, row);
-                    }
+                int good = 1;
+                if (lane == 0) {
+                    if (u > 0 && !mbar_wait(empty, (u - 1) & 1, p.error, ERR_PRODUCER)) good = 0;
+                    if (good) mbar_expect_tx(full, KV_STAGE);
                 }
+                good = __shfl_sync(0xffffffffu, good, 0);
+                if (!good) { ok = false; break; }
+                if (mine)
+                    tma_load_2d(sm + (kv ? OFF_V : OFF_K) + s * KV_STAGE + kb * (BN * 128) + c * p.box_rows * 128,
+                                &cache_map, full, kb * 64, row + kv * kv_step);
             }
-#pragma unroll
-            for (int c = 0; c < 8; ++c) pages[c] = pages_next[c];
-            blk = blk_n; off = off_n;
+            page = page_next; blk = blk_n; off = off_n;
         }
     } else if (warp == 1 && lane == 0) {
         // -------------------------------------------------------------------- MMA issuer
