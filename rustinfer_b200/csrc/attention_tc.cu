@@ -52,9 +52,13 @@ constexpr int KV_STAGE = BN * 128 * KB;           // [KB][64 keys][128 B]
 constexpr int P_BYTES = BM * 128;                 // [128 rows][64 keys] bf16
 constexpr int OFF_Q = 0, OFF_K = OFF_Q + Q_BYTES, OFF_V = OFF_K + NS * KV_STAGE, OFF_P = OFF_V + NS * KV_STAGE;
 constexpr int OFF_BAR = OFF_P + P_BYTES;
-constexpr size_t SMEM = (size_t)OFF_BAR + 512 + 1024 /*alignment*/;
+// No slack for rounding the base up: with heads of 128 two CTAs fit an SM only without it
+// (2 x (112 KB + barriers + 1 KB the system keeps per CTA) of 228 KB).  A kernel without static
+// shared memory gets its dynamic part on a 1024-byte boundary; the kernel checks that and refuses
+// to run otherwise.
+constexpr size_t SMEM = (size_t)OFF_BAR + 128;
 
-enum { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13 };
+enum { ERR_PRODUCER = 11, ERR_MMA = 12, ERR_SOFTMAX = 13, ERR_ALIGNMENT = 14 };
 
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -125,8 +129,11 @@ struct Params {
 // allow it): the other CTAs' softmax fills the issue slots one leaves while it waits on its chain
 __global__ void __launch_bounds__(THREADS, HD == 64 ? 3 : 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap cache_map, const Params p) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char sm[];
+    if ((smem_u32(sm) & 1023u) != 0) {                         // the 128-byte swizzle wants 1024-byte tiles
+        if (threadIdx.x == 0) atomicCAS(p.error, 0, ERR_ALIGNMENT);
+        return;
+    }
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_BAR);
     uint64_t* k_full = bars;              // [NS]
     uint64_t* k_empty = k_full + NS;      // [NS]

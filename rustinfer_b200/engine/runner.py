@@ -531,7 +531,9 @@ class ModelRunner:
         from ..ops import kernels as _k
         code = _k.gemm_tc_error(self.device)
         if code:
-            raise RuntimeError(f"the tensor-core matrix product gave up a wait (code {code}); "
+            what = ("its shared memory did not start on a 1024-byte boundary" if code == 14
+                    else "a bounded wait ran out")
+            raise RuntimeError(f"a tensor-core kernel gave up (code {code}: {what}); "
                                f"results of the last steps are not valid")
 
     def _zero_new_state(self) -> None:
