@@ -28,10 +28,14 @@
 #include "tc_primitives.cuh"
 #include <cuda.h>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #ifndef RI_HEAD_DIM
 #error "compile with -DRI_HEAD_DIM=<head size>"
+#endif
+#ifndef RI_ATTN_POLY_OF
+#define RI_ATTN_POLY_OF (RI_HEAD_DIM == 64 ? 3 : 0)
 #endif
 
 namespace {
@@ -113,6 +117,35 @@ __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 2^x for a pair of x <= 0 without the special-function unit: x = n + f with n the nearest
+// integer, 2^f for f in [-0.5, 0.5] by a polynomial of degree 4 (relative error 2.7e-6, far
+// inside the rounding of a probability to bf16), n added to the exponent.  The unit computes
+// 16 exponentials a clock and SM; a third of a tile's go this way, on the fma pipe, beside it.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+    const float magic = 12582912.f;                            // 1.5 * 2^23: adding it rounds to an integer
+    x.x = fmaxf(x.x, -126.f); x.y = fmaxf(x.y, -126.f);
+    const float2 m2 = make_float2(magic, magic);
+    const float2 xr = __fadd2_rn(x, m2);
+    const float2 n = __fadd2_rn(xr, make_float2(-magic, -magic));
+    const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+    float2 r = make_float2(0.009570098482072353f, 0.009570098482072353f);
+    r = __ffma2_rn(r, f, make_float2(0.05591785907745361f, 0.05591785907745361f));
+    r = __ffma2_rn(r, f, make_float2(0.240247443318367f, 0.240247443318367f));
+    r = __ffma2_rn(r, f, make_float2(0.6931217908859253f, 0.6931217908859253f));
+    r = __ffma2_rn(r, f, make_float2(0.9999992847442627f, 0.9999992847442627f));
+    r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(xr.x) << 23));
+    r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(xr.y) << 23));
+    return r;
+}
+constexpr int POLY_OF = RI_ATTN_POLY_OF;   // one pair of every POLY_OF goes to the polynomial (0: none)
+
+// the larger of three in one instruction
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 struct Params {
@@ -316,7 +349,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap cache_map, const Params 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty);                // the tensor core may write the next tile's scores
-            if (p.window > 0 || t * BN + BN - 1 > p_row || !row_ok) {
+            const bool masked = p.window > 0 || t * BN + BN - 1 > p_row || !row_ok;
+            if (masked) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i) {
                     const int key = t * BN + i;
@@ -327,9 +361,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap cache_map, const Params 
             // row, and a single chain of 64 dependent operations would leave the scheduler idle
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < BN; i += 4) {
-                mx4[0] = fmaxf(mx4[0], s[i]); mx4[1] = fmaxf(mx4[1], s[i + 1]);
-                mx4[2] = fmaxf(mx4[2], s[i + 2]); mx4[3] = fmaxf(mx4[3], s[i + 3]);
+            for (int i = 0; i < BN; i += 8) {
+                mx4[0] = max3(mx4[0], s[i], s[i + 1]); mx4[1] = max3(mx4[1], s[i + 2], s[i + 3]);
+                mx4[2] = max3(mx4[2], s[i + 4], s[i + 5]); mx4[3] = max3(mx4[3], s[i + 6], s[i + 7]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2;
             // The reference maximum moves only when the row's maximum has outgrown it by 2^8
@@ -358,16 +392,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap cache_map, const Params 
             }
             l *= factor;
             const float m_use = m == -INFINITY ? 0.f : m;
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // two scores an instruction where the hardware has one (fma and add on pairs of fp32).
+            // A warp with a masked row in this tile (the diagonal, a window's edge, rows past the
+            // portion) computes every exponential on the special-function unit, which gives an
+            // exact zero for a masked score; the polynomial gives 2^-126 there.
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-m_use, -m_use);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+            auto exponentials = [&](auto with_poly) {
 #pragma unroll
-            for (int i = 0; i < BN; i += 4) {
+                for (int i = 0; i < BN; i += 4) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    s[i + k] = ex2(fmaf(s[i + k], p.scale_log2, -m_use));
-                    sum4[k] += s[i + k];
+                    for (int k = 0; k < 2; ++k) {
+                        const float2 x = __ffma2_rn(make_float2(s[i + 2 * k], s[i + 2 * k + 1]), scale2, shift2);
+                        if (decltype(with_poly)::value && POLY_OF > 0 && ((i / 2 + k) % POLY_OF) == POLY_OF - 1) {
+                            const float2 e = ex2_poly2(x);
+                            s[i + 2 * k] = e.x;
+                            s[i + 2 * k + 1] = e.y;
+                        } else {
+                            s[i + 2 * k] = ex2(x.x);
+                            s[i + 2 * k + 1] = ex2(x.y);
+                        }
+                        sum2[k] = __fadd2_rn(sum2[k], make_float2(s[i + 2 * k], s[i + 2 * k + 1]));
+                    }
                 }
-            }
-            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            };
+            if (__any_sync(0xffffffffu, masked)) exponentials(std::false_type{});
+            else exponentials(std::true_type{});
+            l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
             // P row (bf16) into the A operand of P V
             if (!mbar_wait(p_empty, (j & 1) ^ 1, p.error, ERR_SOFTMAX)) { ok = false; break; }
             {
@@ -485,11 +536,13 @@ RI_API void ri_set_pdl(int on) { ri_pdl_flag() = on ? 1 : 0; }
 RI_API int ri_attention_tc_head_dim() { return HD; }
 
 // 1 if this kernel takes the grouping and page size, else 0 (the caller then uses the
-// mma.sync kernel): the group must divide 128 rows, pages must be 8, 16, 32 or a multiple of 64 keys.
+// mma.sync kernel): a group of at most 128 heads, pages of 8, 16, 32 or a multiple of 64 keys.
+// A tile holds floor(128 / group) tokens; with a group that does not divide 128 the last
+// rows of the tile are padding (a group of 3: 42 tokens, 126 rows), computed and dropped.
 RI_API int ri_attention_tc_supports(int Hq, int Hkv, int page_size) {
     if (Hkv <= 0 || Hq % Hkv != 0) return 0;
     const int G = Hq / Hkv;
-    if (G > BM || BM % G != 0) return 0;
+    if (G > BM) return 0;
     return (page_size == 8 || page_size == 16 || page_size == 32 || (page_size > 0 && page_size % 64 == 0)) ? 1 : 0;
 }
 RI_API int ri_attention_tc_tokens_per_tile(int Hq, int Hkv) { return BM / (Hq / Hkv); }

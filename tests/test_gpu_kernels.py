@@ -536,8 +536,9 @@ def test_attention_mma_finds_one_far_key(kernel):
 
 
 # ------------------------------------------------ tcgen05 prompt attention (bf16, hd 64/128)
+# groups of 3, 5, 7 and 12 heads do not divide the 128 rows of a tile: its last rows are padding
 TC_ATT_SHAPES = [(8, 2, 64, 16), (32, 8, 64, 16), (4, 4, 64, 8), (16, 1, 64, 32), (8, 2, 128, 16), (24, 3, 128, 64),
-                 (2, 2, 128, 8)]
+                 (2, 2, 128, 8), (6, 2, 128, 16), (24, 8, 128, 16), (5, 1, 64, 16), (14, 2, 64, 32), (12, 1, 128, 8)]
 
 
 @pytest.mark.parametrize("Hq,Hkv,hd,page", TC_ATT_SHAPES)

@@ -40,8 +40,8 @@ PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16, "F": 8, "Bs": 8}
 
 def expect_fast_kernels(r, name):
     """In bfloat16 the models with head sizes 64 and 128 must run on the kernels made for
-    them: keys and values by TMA when decoding, tcgen05 for prompt portions where the group
-    size lets it, and the chained products for steps of few tokens."""
+    them: keys and values by TMA when decoding, tcgen05 for prompt portions (a group of 3 heads
+    included: 42 tokens a tile and two rows of padding), and the chained products for steps of few tokens."""
     if name not in FAST or r.dtype != torch.bfloat16:
         return
     from rustinfer_b200.ops import library
@@ -50,7 +50,7 @@ def expect_fast_kernels(r, name):
         lib = library.attention_mma(a.hd)
         tma = int(lib.ri_attention_decode_tma_ctas_per_sm(r.page_size))
         assert tma > 0 and a.decode_ctas_per_sm == tma, "decode attention does not fetch by TMA"
-        assert a.use_tc == (128 % (a.Hq // a.Hkv) == 0), "prompt attention is not on tcgen05"
+        assert a.use_tc, "prompt attention is not on tcgen05"
     assert r.model.chained is not None and r.model.chained.max_tokens >= 16
 
 
