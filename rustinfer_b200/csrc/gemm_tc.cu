@@ -76,6 +76,12 @@ struct Params {
     int stages, stage_bytes;             // ring of operand stages: (a_box + BN) * 128 bytes each
     int budget;                          // bytes of the ring
     int pair_bn;                         // width of a CTA pair's tile (256 or 192)
+    // CTA pairs, the tiles of the last, partly filled wave: their k-blocks are dealt out evenly
+    // over all pairs (each pair a run of k-blocks that meets one or two of those tiles); the
+    // parts of a tile are added up in `sk_acc` and the pair that adds last finishes the tile
+    int sk_tiles;                        // tiles dealt out that way (0: none), the last of n_tiles
+    int sk_pairs, sk_q, sk_extra;        // pairs that take part; k-blocks of each: sk_q, the first sk_extra one more
+    float* sk_acc;                       // [pair][first or second tile of its run][2 CTAs][4 warps][width/4][32 lanes][4] fp32
 };
 
 
@@ -87,7 +93,7 @@ __device__ __forceinline__ void store_one(const Params& p, int n_tok, int n_feat
     switch (p.epilogue) {
         case EPI_BF16: reinterpret_cast<bf16*>(p.out)[row + feat] = __float2bfloat16_rn(acc); break;
         case EPI_F32: reinterpret_cast<float*>(p.out)[row + feat] = acc; break;
-        case EPI_RESIDUAL: reinterpret_cast<float*>(p.out)[row + feat] += acc; break;
+        case EPI_RESIDUAL: atomicAdd(reinterpret_cast<float*>(p.out) + row + feat, acc); break;   // parts of one sum may come from several CTAs
         case EPI_SILU:                                   // even feature = gate_j, odd = up_j
             if ((feat & 1) == 0)
                 reinterpret_cast<bf16*>(p.out)[row + (feat >> 1)] = __float2bfloat16_rn(silu_mul(acc, neighbour));
@@ -504,11 +510,41 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, unsigned rank)
                  ::"r"(smem_u32(bar)), "r"(rank) : "memory");
 }
 
+// What a pair works on next: a whole tile, or a run of k-blocks of one of the dealt-out tiles.
+struct PairItem { int tile, kb0, kb1, part; };
+// first k-block (counted through the dealt-out tiles) of a pair's run
+__device__ __forceinline__ int sk_start(const Params& p, int pair) {
+    return pair * p.sk_q + min(pair, p.sk_extra);
+}
+// the pair whose run holds k-block `step`
+__device__ __forceinline__ int sk_pair_of(const Params& p, int step) {
+    const int wide = p.sk_extra * (p.sk_q + 1);
+    return step < wide ? step / (p.sk_q + 1) : p.sk_extra + (step - wide) / p.sk_q;
+}
+// Item `idx` of a pair: first its share of the dealt-out tiles (their sums are finished by
+// whichever pair comes last, behind the whole tiles that follow), then whole tiles pair, pair + pairs, ...
+__device__ __forceinline__ bool pair_item(const Params& p, int pair, int pairs, int n_kb, int idx, PairItem& it) {
+    const int whole = p.n_tiles - p.sk_tiles;
+    int n_seg = 0;
+    if (p.sk_tiles > 0 && pair < p.sk_pairs) {
+        const int s0 = sk_start(p, pair), s1 = sk_start(p, pair + 1);
+        const int r = s0 / n_kb, k0 = s0 - r * n_kb;
+        const int len0 = min(s1 - s0, n_kb - k0);
+        n_seg = len0 < s1 - s0 ? 2 : 1;
+        if (idx == 0) { it.tile = whole + r; it.kb0 = k0; it.kb1 = k0 + len0; it.part = 1; return true; }
+        if (idx == 1 && n_seg == 2) { it.tile = whole + r + 1; it.kb0 = 0; it.kb1 = s1 - s0 - len0; it.part = 1; return true; }
+    }
+    const int tile = pair + (idx - n_seg) * pairs;
+    if (tile >= whole) return false;
+    it.tile = tile; it.kb0 = 0; it.kb1 = n_kb; it.part = 0;
+    return true;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const Params p) {
     constexpr int ACC_COLS = 256, TMEM_COLS = 512;
-    const int BN = p.pair_bn, HALF_BN = BN >> 1;                  // 256, or 192 where that evens out the waves
+    const int BN = p.pair_bn, HALF_BN = BN >> 1;                  // 128 to 256, whichever evens out the waves
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -548,9 +584,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         int it = 0, s = 0;
         unsigned par = 1;
-        for (int tile = pair; tile < p.n_tiles && ok; tile += pairs) {
+        PairItem item;
+        for (int idx = 0; ok && pair_item(p, pair, pairs, n_kb, idx, item); ++idx) {
+            const int tile = item.tile;
             const int a0 = (tile % p.tiles_a) * 256 + (int)rank * BM, b0 = (tile / p.tiles_a) * BN + (int)rank * HALF_BN;
-            for (int i = 0; i < n_kb; ++i, ++it) {
+            for (int i = item.kb0; i < item.kb1; ++i, ++it) {
                 unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
                 if (it >= STAGES && (s & 1) == 0 &&
                     !mbar_try_wait(&empty[s >> 1], par) && !mbar_wait(&empty[s >> 1], par, p.error, ERR_PRODUCER_WAIT)) { ok = false; break; }
@@ -569,18 +607,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         int s = 0, t = 0;
         unsigned par = 0;
-        for (int tile = pair; tile < p.n_tiles && ok; tile += pairs, ++t) {
+        PairItem item;
+        for (int idx = 0; ok && pair_item(p, pair, pairs, n_kb, idx, item); ++idx, ++t) {
             const int buf = t & 1, use = t >> 1;
             if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, p.error, ERR_MMA_WAIT)) { ok = false; break; }
             tc_fence_after();
             const unsigned tmem_d = tmem_base + buf * ACC_COLS;
-            for (int i = 0; i < n_kb; ++i) {
+            for (int i = item.kb0; i < item.kb1; ++i) {
                 if (!mbar_try_wait(&full[s], par) && !mbar_wait(&full[s], par, p.error, ERR_MMA_WAIT)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t da = desc0 + (uint64_t)(s * stage_step), db = da + (uint64_t)b_step;
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)
-                    mma_bf16_ss_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    mma_bf16_ss_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (i > item.kb0 || k > 0) ? 1u : 0u);
                 if (s & 1) tc_commit_pair(&empty[s >> 1]);
                 if (++s == STAGES) { s = 0; par ^= 1u; }
             }
@@ -599,36 +638,100 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         bool ok = true;
         int t = 0;
         pdl_wait();
-        for (int tile = pair; tile < p.n_tiles; tile += pairs, ++t) {
+        PairItem item;
+        for (int idx = 0; pair_item(p, pair, pairs, n_kb, idx, item); ++idx, ++t) {
+            const int tile = item.tile;
             const int a0 = (tile % p.tiles_a) * 256 + (int)rank * BM, b0 = (tile / p.tiles_a) * BN;
             const int ra = a0 + quarter * 32 + lane;
             const int buf = t & 1, use = t >> 1;
             if (ok) ok = mbar_wait(&acc_full[buf], use & 1, p.error, ERR_EPILOGUE_WAIT);
             tc_fence_after();
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + buf * ACC_COLS;
-            if (ok) {
-                // 64 columns a round trip to tensor memory where the tile lies inside the matrix
-                // (the width is 192 or 256): the epilogue of a pair's last tile has no MMA to hide
-                // behind.  At the ragged edge 16 at a time, element by element.
+            // Part of a tile's sum over K.  Added into the fp32 stream it needs no meeting point
+            // (the stores below are reductions at the memory side).  Otherwise the part goes to
+            // this pair's slot of the meeting buffer, and the warp that comes last (a ticket per
+            // tile, CTA and warp: the same rows come from the same warp of every pair) adds the
+            // parts in the order of the pairs, so the sum does not depend on who came last.  The
+            // accumulator in tensor memory is given back before that: the whole tiles that follow
+            // hide the meeting.
+            const bool meet = item.part && p.epilogue != EPI_RESIDUAL;
+            const int sk_tile = tile - (p.n_tiles - p.sk_tiles);
+            const size_t warp_floats = (size_t)BN * 32, slot_floats = warp_floats * 8;
+            const size_t warp_off = (size_t)((int)rank * 4 + quarter) * warp_floats + lane * 4;
+            bool finish = ok;
+            int first_pair = 0, parts = 0;
+            if (meet && ok) {
+                const int seg = sk_start(p, pair) < sk_tile * n_kb ? 1 : 0;      // this tile is the second one of the run
+                float* mine = p.sk_acc + (size_t)(pair * 2 + seg) * slot_floats + warp_off;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 64) {
-                    if (p.vec && b0 + c0 + 64 <= p.b_rows) {
-                        float v[64];
+                    float v[64];
+                    tmem_ld_row<64>(taddr + c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        __stcg(reinterpret_cast<float4*>(mine + (size_t)(c0 / 4 + j) * 128),
+                               make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+                }
+                // (the accumulator is free as soon as it is in registers; the fence below waits
+                // for the stores, and the MMA thread should not wait with it)
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(&acc_empty[buf], 0);
+                __threadfence();
+                __syncwarp();
+                first_pair = sk_pair_of(p, sk_tile * n_kb);
+                parts = sk_pair_of(p, sk_tile * n_kb + n_kb - 1) - first_pair + 1;
+                const int slot = (sk_tile * 2 + (int)rank) * 4 + quarter;
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(&p.counters[slot], 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                finish = ticket == parts - 1;
+                if (finish) {
+                    __threadfence();
+                    if (lane == 0) p.counters[slot] = 0;
+                }
+            }
+            if (finish) {
+                // 64 columns a round trip to tensor memory where the tile lies inside the matrix:
+                // the epilogue of a pair's last tile has no MMA to hide behind.  At the ragged
+                // edge 16 at a time, element by element.
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    float v[64];
+                    if (meet) {
+#pragma unroll
+                        for (int j = 0; j < 64; ++j) v[j] = 0.f;
+#pragma unroll 1
+                        for (int pr = first_pair; pr < first_pair + parts; ++pr) {
+                            const int seg = sk_start(p, pr) < sk_tile * n_kb ? 1 : 0;
+                            const float* src = p.sk_acc + (size_t)(pr * 2 + seg) * slot_floats + warp_off;
+                            float4 x[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) x[j] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(c0 / 4 + j) * 128));
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                v[4 * j] += x[j].x; v[4 * j + 1] += x[j].y; v[4 * j + 2] += x[j].z; v[4 * j + 3] += x[j].w;
+                            }
+                        }
+                    } else {
                         tmem_ld_row<64>(taddr + c0, v);
+                    }
+                    if (p.vec && b0 + c0 + 64 <= p.b_rows) {
                         store_row64(p, ra, b0 + c0, v);
                     } else {
-#pragma unroll 1
-                        for (int c1 = c0; c1 < c0 + 64; c1 += 16) {
-                            float v[16];
-                            tmem_ld16(taddr + c1, v);
-                            store_row16(p, ra, b0 + c1, v);
+#pragma unroll
+                        for (int c1 = 0; c1 < 64; c1 += 16) {
+                            float w[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) w[j] = v[c1 + j];
+                            store_row16(p, ra, b0 + c0 + c1, w);
                         }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_remote(&acc_empty[buf], 0);      // the even CTA's MMA thread counts all eight warps
+            if (lane == 0 && !(meet && ok)) mbar_arrive_remote(&acc_empty[buf], 0);   // the even CTA's MMA thread counts all eight warps
         }
     }
     tc_fence_before();
@@ -650,7 +753,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const Params& p, c
         configured = true;
     }
     const int sms = device_sms();
-    const int pairs = p.n_tiles < sms / 2 ? p.n_tiles : sms / 2;
+    const int pairs = (p.sk_tiles == 0 && p.n_tiles < sms / 2) ? p.n_tiles : sms / 2;
     RI_CHECKED(ri_launch(gemm_tc_pair_kernel, dim3(2 * pairs), dim3(THREADS), (size_t)p.budget + SMEM_EXTRA, s, ma, mb, p));
     return ri_launch_status();
 }
@@ -702,9 +805,11 @@ RI_API void ri_gemm_tc_set_stream_budget(int bytes) {
 
 // a_box: rows of the 128-row operand a tile really covers (a multiple of 8 from 8 to 128;
 // fewer than 128 evens out the last wave of tiles over the SMs).
+// sk_acc: SMs x 65536 floats where the parts of tiles that several CTA pairs share meet (two
+// 256 x 256 fp32 tiles a pair); null: every tile stays with one pair.
 RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* out, int ld_out, int epilogue,
                       int swap, int bn, int splits, int a_box, float* workspace, int* counters, int* error,
-                      void* stream) {
+                      float* sk_acc, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || splits < 1 || (splits > 1 && (!workspace || !counters)) || !error ||
         a_box < 8 || a_box > BM || a_box % 8 != 0)
@@ -713,6 +818,7 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     const void* B = swap ? X : W;
     Params p;
     p.pair_bn = 0;
+    p.sk_tiles = p.sk_pairs = p.sk_q = p.sk_extra = 0; p.sk_acc = nullptr;
     p.a_rows = swap ? N : M;
     p.b_rows = swap ? M : N;
     p.K = K; p.swap = swap; p.epilogue = epilogue; p.out = out; p.ld_out = ld_out; p.splits = splits;
@@ -740,18 +846,49 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     // many tokens: a 256 x 256 tile on a CTA pair (less operand traffic per flop)
     static const bool pair_off = getenv("RUSTINFER_B200_GEMM_PAIR") && atoi(getenv("RUSTINFER_B200_GEMM_PAIR")) == 0;
     if (!swap && bn == PAIR_BN && splits == 1 && a_box == BM && !pair_off && p.a_rows >= 512) {
-        // the width of a tile: 256, or 192 where fewer columns in the last wave of tiles cost less
-        // than narrower tiles do (3072 features of 2048 tokens: 96 tiles of 256 are two waves on
-        // 74 pairs, 512 columns deep; 128 tiles of 192 are two waves too, 384 deep)
+        // A tile is 256 rows by 256 columns, or by 192 where that fills the waves better.  The
+        // k-blocks of a last wave that would leave pairs idle can be dealt out over all pairs
+        // (3072 features of 2048 tokens, K = 8192: 96 tiles of 256 on 74 pairs are two waves,
+        // 256 k-blocks a pair; dealt out, 74 whole tiles and 22 x 128 / 74 = 38 k-blocks each).
+        // A k-block costs a pair about the same time at both widths, so the count decides.
+        // Dealing is not free: every part is a whole 256 x 256 fp32 tile that has to go
+        // somewhere.  A product that is added into the fp32 stream adds its parts where the
+        // whole would go (reductions at the memory side, measured to cost about 24 k-blocks);
+        // any other one leaves them in the buffer, and the pairs that finish a tile read four or
+        // five parts back from L2 under the operands' traffic (about 40 k-blocks).  So only a
+        // long K with a short last wave is dealt: the 3B shape's down projection, 97 -> 79 us.
         p.tiles_a = (p.a_rows + 255) / 256;
         const int pairs = device_sms() / 2;
-        long long best = 0;
-        p.pair_bn = PAIR_BN;
+        const int n_kb = (K + BK - 1) / BK;
+        const int meeting = epilogue == EPI_RESIDUAL ? 24 : 40;
+        static const bool deal_off = getenv("RUSTINFER_B200_GEMM_DEAL") && atoi(getenv("RUSTINFER_B200_GEMM_DEAL")) == 0;
+        if (deal_off) sk_acc = nullptr;
+        long long best = -1;
         for (int w : {256, 192}) {
-            const long long tiles = (long long)p.tiles_a * ((p.b_rows + w - 1) / w);
-            const long long depth = ((tiles + pairs - 1) / pairs) * w;
-            if (best == 0 || depth < best) { best = depth; p.pair_bn = w; }
+            const int tiles = p.tiles_a * ((p.b_rows + w - 1) / w);
+            const int waves = tiles / pairs, rest = tiles % pairs;
+            for (int deal = 0; deal < 2; ++deal) {
+                // (a run of k-blocks meets two tiles at most)
+                if (deal && (rest == 0 || !sk_acc || n_kb < 8 || waves == 0)) continue;
+                long long cost;
+                int q = 0, extra = 0, takers = 0;
+                if (!deal) {
+                    cost = (long long)(waves + (rest ? 1 : 0)) * n_kb * 16;
+                } else {
+                    const int steps = rest * n_kb;
+                    takers = steps / 4 < pairs ? steps / 4 : pairs;       // at least four k-blocks a pair
+                    if (takers < 1) continue;
+                    q = steps / takers; extra = steps % takers;
+                    cost = ((long long)waves * n_kb + q + (extra ? 1 : 0) + meeting) * 16;
+                }
+                cost += w == 192 ? 1 : 0;                                  // equal counts: the wider tile
+                if (best < 0 || cost < best) {
+                    best = cost; p.pair_bn = w;
+                    p.sk_tiles = deal ? rest : 0; p.sk_pairs = takers; p.sk_q = q; p.sk_extra = extra;
+                }
+            }
         }
+        p.sk_acc = sk_acc;
         p.stage_bytes = (BM + p.pair_bn / 2) * BK * 2;
         p.stages = (p.budget / p.stage_bytes) & ~1;
         if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;

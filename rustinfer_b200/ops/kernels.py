@@ -129,13 +129,16 @@ _TC_COUNTERS = 1 << 14
 
 
 def gemm_tc_state(device: torch.device):
-    """(workspace fp32, tile counters int32, error flag int32) of the tensor-core GEMM on a
-    device; made once, so that captured graphs keep valid addresses."""
+    """(workspace fp32, tile counters int32, error flag int32, meeting buffer fp32) of the
+    tensor-core GEMM on a device; made once, so that captured graphs keep valid addresses.
+    The meeting buffer (two 256 x 256 fp32 tiles per pair of SMs) is where CTA pairs that
+    share a tile's sum over K leave their parts."""
     st = _tc_state.get(device)
     if st is None:
         st = (torch.empty(_TC_WORKSPACE_FLOATS, dtype=torch.float32, device=device),
               torch.zeros(_TC_COUNTERS, dtype=torch.int32, device=device),
-              torch.zeros(1, dtype=torch.int32, device=device))
+              torch.zeros(1, dtype=torch.int32, device=device),
+              torch.zeros(L.num_sms() * 65536, dtype=torch.float32, device=device))
         _tc_state[device] = st
     return st
 
@@ -202,13 +205,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
     plan = plan or gemm_tc_plan(M, N, Kd, num_sms, epilogue)
     swap, bn, splits = plan[:3]
     a_box = plan[3] if len(plan) > 3 else 128
-    ws, counters, err = gemm_tc_state(x.device)
+    ws, counters, err, meeting = gemm_tc_state(x.device)
     tiles = (-(-N // a_box)) * (-(-M // bn)) if swap else (-(-M // a_box)) * (-(-N // bn))
     meets = splits > 1 and epilogue != EPI_RESIDUAL
     if tiles > counters.numel() or (meets and tiles * splits * bn * 128 > ws.numel()):
         raise KernelError("gemm_tc: the split-K workspace is too small for this plan")
     check(L.gemm_tc().ri_gemm_tc(_p(x), _p(w), M, N, Kd, _p(out), out.stride(0), epilogue, swap, bn, splits,
-                                 a_box, _p(ws), _p(counters), _p(err), stream_ptr()), "gemm_tc")
+                                 a_box, _p(ws), _p(counters), _p(err), _p(meeting), stream_ptr()), "gemm_tc")
 
 
 class _ChainPhase(ctypes.Structure):
@@ -351,7 +354,7 @@ def decode_chain(products: Sequence[ChainProduct], rope: Optional[ChainRope], to
         rs = _ChainRope()
         rope.fill(rs)
         rp = ctypes.cast(ctypes.pointer(rs), ctypes.c_void_p)
-    _, _, err = gemm_tc_state(dev)
+    err = gemm_tc_state(dev)[2]
     check(L.gemm_tc().ri_decode_chain(ctypes.cast(arr, ctypes.c_void_p), len(products), rp, tokens,
                                       _p(_chain_barrier(dev)), _p(err), num_sms, stream_ptr()), "decode_chain")
 
@@ -436,7 +439,7 @@ def attention_prefill_tc(q, out, cache, block_table, cu_q, kv_len, tile_entry, t
     _i32(tile_entry, "tile_entry"); _i32(tile_tok0, "tile_tok0")
     if out.stride(0) % 8 or out.data_ptr() % 16 or cache.data_ptr() % 16:
         raise KernelError("attention_prefill_tc: out rows and the cache must be 16-byte aligned")
-    _ws, _counters, err = gemm_tc_state(q.device)
+    err = gemm_tc_state(q.device)[2]
     lib = L.attention_tc(head_dim)
     check(lib.ri_attention_prefill_tc(_p(q), q.stride(0), _p(out), out.stride(0), _p(cache), cache.shape[0],
                                       _p(block_table), block_table.stride(0), _p(cu_q), _p(kv_len),

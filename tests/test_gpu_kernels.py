@@ -126,7 +126,9 @@ def test_gemm_f32_is_exact_fp32(M, N, K_):
 # in any direction; the last one has several waves of the narrower tile
 TC_SHAPES = [(1, 130, 96), (8, 3072, 2048), (17, 544, 96), (64, 391, 272), (65, 391, 272), (300, 130, 104),
              (200, 1000, 72), (128, 256, 64), (5, 16, 8), (512, 512, 256), (1000, 4000, 520), (777, 264, 72),
-             (2040, 3080, 136)]
+             (2040, 3080, 136),
+             # many tokens: tiles of a CTA pair, 256 rows by 240, 192 and 224 columns (whatever evens out the waves)
+             (2048, 2048, 72), (2048, 5120, 72), (1536, 2500, 72)]
 
 
 @pytest.mark.parametrize("epi", ["bf16", "f32", "silu", "residual"])
@@ -161,6 +163,49 @@ def test_gemm_tc_against_float64(M, N, K_, epi):
         close(out, ref, torch.bfloat16)
     torch.cuda.synchronize()
     assert k.gemm_tc_error(dev()) == 0
+
+
+@pytest.mark.parametrize("M,N,K_", [(2048, 2560, 4096), (2040, 2500, 4104), (2048, 3072, 8192)])
+def test_gemm_tc_dealt_last_wave(M, N, K_):
+    """Many tokens, a long K and a last wave of few tiles: the k-blocks of those tiles are dealt
+    out over all CTA pairs and the parts meet in a buffer (or, added into the fp32 stream, where
+    the whole would go).  Every epilogue; the same bits whichever pair finishes a tile."""
+    torch.manual_seed(N)
+    k = K()
+    x = torch.randn(M, K_, device=dev()).bfloat16()
+    w = (torch.randn(N, K_, device=dev()) / math.sqrt(K_)).bfloat16()
+    ref = (x.double() @ w.double().T).cpu()                  # the oracle: a float64 product
+    outs = []
+    for _ in range(3):
+        out = torch.full((M, N), float("nan"), device=dev())
+        k.gemm_tc(x, w, out, k.EPI_F32)
+        outs.append(out)
+    # a sum of K products kept in fp32: |err| <= (K + 2) 2^-24 sum |x||w| (one rounding per
+    # addition and per part); a k-block left out or added twice would be off by about 0.1
+    bound = (K_ + 2) * 2.0 ** -24 * float((x.double().abs() @ w.double().abs().T).max())
+    err = float((outs[0].double().cpu() - ref).abs().max())
+    assert err <= bound, f"max err {err:.3e} vs bound {bound:.3e}"
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    k.gemm_tc(x, w, out, k.EPI_BF16)
+    assert torch.equal(out, outs[0].bfloat16())              # the same sum, rounded once
+    out = torch.full((M, N // 2), float("nan"), dtype=torch.bfloat16, device=dev())
+    k.gemm_tc(x, w, out, k.EPI_SILU)
+    f = outs[0].double().cpu()
+    close(out, P.swiglu(f[:, 0::2], f[:, 1::2]), torch.bfloat16)
+    base = torch.randn(M, N, device=dev())
+    h = base.clone()
+    k.gemm_tc(x, w, h, k.EPI_RESIDUAL)
+    err = float((h.double().cpu() - (ref + base.double().cpu())).abs().max())
+    assert err <= bound + 2.0 ** -23 * float(h.abs().max()), f"max err {err:.3e} vs bound {bound:.3e}"
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+    # the counters are left zero: a second product of another shape right behind it
+    x2 = torch.randn(70, 1032, device=dev()).bfloat16()
+    w2 = (torch.randn(300, 1032, device=dev()) / 32).bfloat16()
+    out2 = torch.full((70, 300), float("nan"), device=dev())
+    k.gemm_tc(x2, w2, out2, k.EPI_F32, (1, 16, 7))
+    close(out2, (x2.double() @ w2.double().T).cpu(), torch.float32)
 
 
 @pytest.mark.parametrize("plan", [(1, 16, 1), (1, 16, 7), (1, 64, 3), (0, 16, 1), (0, 128, 2), (0, 256, 1), (0, 64, 5),
