@@ -144,7 +144,10 @@ class ChainedDecoder:
             rows = K.CHAIN_MAX_TOKENS
             # up to 16 single tokens whose keys were cut into ranges: the output product merges the
             # ranges itself while it lays out its operand, and the attention launches no merge
-            ranges = a.unmerged_ranges(step) if (step is not None and T <= 16 and self.fold_merge) else 0
+            # (heads of 64: the 1B shape's step 1.061 -> 1.054 ms.  With heads of 128 the operand's
+            # lay-out takes twice as long and the 8B shape's step went from 1.40 to 1.47 ms, so those
+            # keep the merge launch.)
+            ranges = a.unmerged_ranges(step) if (step is not None and T <= 16 and self.fold_merge and a.hd <= 64) else 0
             partials = (a.part_o, a.part_lse, ranges, a.Hq, a.hd) if ranges else None
             products = [K.ChainProduct(a.o.weight, attn[:T], self.h[:T], K.CHAIN_ADD_F32, x_rows=rows, partials=partials),
                         K.ChainProduct(f.gate_up.weight, self.h[:T], mid[:T], K.CHAIN_SILU_BF16,
