@@ -56,6 +56,8 @@ class Decoder:
         seen: Dict = {}
         for b in self.blocks:
             for part in (b.mixer, b.ffn):
+                if part is None:
+                    continue
                 for need in part.step_indices():
                     seen.setdefault(need.key, need)
         return list(seen.values())

@@ -37,14 +37,18 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: how mixer, feed-forward and norms are arranged, and the tensor-name
-    prefix of each (`names[role] + local_name` is the tensor's name in the file)."""
+    """One block: which parts it has, how they are arranged, and the tensor-name prefix of
+    each (`names[role] + local_name` is the tensor's name in the file).  Only the mixer is
+    required: a block of one sublayer has no feed-forward, a block whose sublayers share a
+    norm names one, and norms beyond the two usual ones (after a sublayer, say) go by a role
+    of their own in `extra_norms`.  What the arrangement does with them is its business."""
     mixer: PartSpec
-    mixer_norm: PartSpec
-    ffn: PartSpec
-    ffn_norm: PartSpec
-    names: Mapping[str, str]            # roles: mixer, mixer_norm, ffn, ffn_norm
+    mixer_norm: Optional[PartSpec] = None
+    ffn: Optional[PartSpec] = None
+    ffn_norm: Optional[PartSpec] = None
+    names: Mapping[str, str] = field(default_factory=dict)   # role -> prefix; roles: mixer, mixer_norm, ffn, ffn_norm, extras
     arrangement: str = "pre_norm"
+    extra_norms: Mapping[str, PartSpec] = field(default_factory=dict)   # role -> norm
 
 
 @dataclass(frozen=True)

@@ -373,6 +373,123 @@ def test_run_order_shared_cache_and_window_group(tmp_path, dtype):
     assert r.cache.free_pages() == {0: 40, 1: 40}
 
 
+# ------------------------------------------------ other shapes of a block, from this file alone
+# A layer needs only a mixer: here one block runs attention and feed-forward side by side off
+# one norm, one has a single sublayer, and one norms what its sublayers return (norms under
+# roles of their own) before it is added.  The arrangements are registered below; the
+# framework's files know none of them.
+def _register_shapes():
+    from rustinfer_b200.config.registry import ArchitectureFamily, register_architecture
+    from rustinfer_b200.parts.block import register_arrangement
+    from rustinfer_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
+
+    def settle(hidden):
+        """the stream with everything pending added (fp32)"""
+        if hidden.pending is not None:
+            hidden.stream += hidden.pending.float()
+            hidden.pending = None
+        return hidden.stream
+
+    def parallel(block, hidden, step, cache):
+        x = block.mixer_norm.add_norm(hidden.stream, hidden.pending)
+        a = block.mixer.forward(x, step, cache)
+        hidden.stream += a.float()
+        hidden.pending = block.ffn.forward(x, step)
+
+    def mixer_only(block, hidden, step, cache):
+        x = block.mixer_norm.add_norm(hidden.stream, hidden.pending)
+        hidden.pending = block.mixer.forward(x, step, cache)
+
+    def sandwich(block, hidden, step, cache):
+        x = block.mixer_norm.add_norm(hidden.stream, hidden.pending)
+        a = block.mixer.forward(x, step, cache)
+        zeros = torch.zeros_like(hidden.stream)
+        hidden.pending = block.extra_norms["after_mixer"].add_norm(zeros, a)
+        x = block.ffn_norm.add_norm(hidden.stream, hidden.pending)
+        m = block.ffn.forward(x, step)
+        hidden.pending = block.extra_norms["after_ffn"].add_norm(torch.zeros_like(hidden.stream), m)
+
+    register_arrangement("toy_parallel", parallel)
+    register_arrangement("toy_mixer_only", mixer_only)
+    register_arrangement("toy_sandwich", sandwich)
+
+    def spec_of(cfg):
+        d, hd, Hq, Hkv = cfg["hidden_size"], 16, cfg["hidden_size"] // 16, 2
+        norm = PartSpec("rmsnorm", {"size": d, "eps": 1e-5})
+        ffn = PartSpec("swiglu", {"hidden_size": d, "intermediate_size": cfg["intermediate_size"]})
+        rope = PartSpec("rope", {"head_dim": hd, "rotary_dim": hd, "theta": 10000.0, "scaling": None})
+        att = PartSpec("gqa_attention", {"hidden_size": d, "num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd,
+                                         "scale": 0.25, "window": None, "position": rope})
+        layers = (
+            LayerSpec(mixer=att, mixer_norm=norm, ffn=ffn, arrangement="toy_parallel",
+                      names={"mixer": "l0.att.", "mixer_norm": "l0.n.", "ffn": "l0.mlp."}),
+            LayerSpec(mixer=att, mixer_norm=norm, arrangement="toy_mixer_only",
+                      names={"mixer": "l1.att.", "mixer_norm": "l1.n."}),
+            LayerSpec(mixer=att, mixer_norm=norm, ffn=ffn, ffn_norm=norm, arrangement="toy_sandwich",
+                      extra_norms={"after_mixer": norm, "after_ffn": norm},
+                      names={"mixer": "l2.att.", "mixer_norm": "l2.n1.", "ffn": "l2.mlp.", "ffn_norm": "l2.n2.",
+                             "after_mixer": "l2.p1.", "after_ffn": "l2.p2."}),
+        )
+        return ModelSpec(hidden_size=d, vocab_size=cfg["vocab_size"], layers=layers,
+                         run_order=tuple(RunEntry(i) for i in range(3)), final_norm=norm, embed_name="embed.",
+                         final_norm_name="norm.", head_name="head.", tie_head=False)
+
+    register_architecture(["ShapesToyLM"], ArchitectureFamily("shapes", lambda c, g: dict(c), spec_of))
+
+
+def _shapes_plain(cfg, w, ids):
+    d, hd, Hkv = cfg["hidden_size"], 16, 2
+    Hq, T = d // hd, len(ids)
+    f = P.rope_inv_freq(hd, 10000.0, None)
+    pos = torch.arange(T)
+
+    def attention(x, p):
+        q = P.rope_rotate((x @ w[p + "q_proj.weight"].T).view(T, Hq, hd), pos, f)
+        k = P.rope_rotate((x @ w[p + "k_proj.weight"].T).view(T, Hkv, hd), pos, f)
+        v = (x @ w[p + "v_proj.weight"].T).view(T, Hkv, hd)
+        return P.causal_gqa_attention(q, k, v, 0.25, None).reshape(T, d) @ w[p + "o_proj.weight"].T
+
+    def mlp(x, p):
+        return P.swiglu(x @ w[p + "gate_proj.weight"].T, x @ w[p + "up_proj.weight"].T) @ w[p + "down_proj.weight"].T
+
+    h = P.embedding(w["embed.weight"], ids)
+    x = P.rmsnorm(h, w["l0.n.weight"], 1e-5)
+    h = h + attention(x, "l0.att.") + mlp(x, "l0.mlp.")
+    h = h + attention(P.rmsnorm(h, w["l1.n.weight"], 1e-5), "l1.att.")
+    h = h + P.rmsnorm(attention(P.rmsnorm(h, w["l2.n1.weight"], 1e-5), "l2.att."), w["l2.p1.weight"], 1e-5)
+    h = h + P.rmsnorm(mlp(P.rmsnorm(h, w["l2.n2.weight"], 1e-5), "l2.mlp."), w["l2.p2.weight"], 1e-5)
+    return P.rmsnorm(h, w["norm.weight"], 1e-5) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_blocks_of_other_shapes(tmp_path, dtype):
+    from rustinfer_b200.engine.runner import ModelRunner, StepEntry
+    from rustinfer_b200.weights.random_init import write_random_model
+    _register_shapes()
+    cfg = {"architectures": ["ShapesToyLM"], "hidden_size": 64, "intermediate_size": 96, "vocab_size": 113}
+    folder = write_random_model(str(tmp_path / "shapes"), cfg, seed=5, std=0.2, norm_std=0.2)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    _, w = P.read_model_folder(folder)
+    assert "l1.mlp.gate_proj.weight" not in w and "l0.n2.weight" not in w and "l2.p2.weight" in w
+    r = ModelRunner(folder, dtype=dtype, max_model_len=128, page_size=8, num_pages=24, max_batch_seqs=2,
+                    max_batch_tokens=128, capture_sizes=[1, 2])
+    assert r.model.chained is None                             # not the shape the chained products know
+    g = torch.Generator().manual_seed(2)
+    ids = torch.randint(0, 113, (50,), generator=g).tolist()
+    ref = _shapes_plain(cfg, w, ids)
+    tol = LOGITS_TOL[dtype]
+    for cuts in ([50], [9, 30, 2] + [1] * 9):
+        r.open("a")
+        outs, at = [], 0
+        for c in cuts:
+            outs.append(r.step([StepEntry("a", ids[at: at + c], list(range(c)))]))
+            at += c
+        assert rel_err(torch.cat(outs), ref) <= tol, cuts
+        r.close("a")
+    assert r.graph_replays > 0                                 # single tokens were captured and replayed
+
+
 # ------------------------------------------------ toy parts of every kind, from this file alone
 # A stem with a multiplier and learned positions, a head with a soft cap, another rotary law, a
 # feed-forward that routes each token to one of three experts, attention without any position
