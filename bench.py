@@ -472,6 +472,8 @@ def main() -> int:
                          "prompt portions of 512, through Engine.generate")
     ap.add_argument("--eager", action="store_true", help="with --only decode: no CUDA graphs")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
+    ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS,
+                    help="with --only prefill: length of the prompt, computed in one step (up to 8192)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: --gpus {args.gpus} is not supported by this engine")
@@ -506,16 +508,18 @@ def main() -> int:
             return 0
         if args.only:
             seqs = max(args.batch, 1)
+            longest = max(CONTEXT, min(args.prompt_tokens, 8192))
             engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=seqs,
-                            max_model_len=CONTEXT, paged_block_size=PAGE, num_blocks=seqs * CONTEXT // PAGE + 64,
+                            max_model_len=longest, paged_block_size=PAGE, num_blocks=seqs * longest // PAGE + 64,
                             capture_sizes=[] if args.eager else [1, 2, 4, 8, 16, 32, 64], ignore_eos=True)
             if args.only == "decode":
                 global_ctx = args.context
                 ms, n, _ = decode_device_timed(engine, args.batch, args.steps, args.warmup, vocab, 1, global_ctx)
                 print(f"decode b{args.batch} ctx{global_ctx} layers{args.layers}: {ms:.4f} ms/step, {n} launches")
             else:
-                ms, _ = prefill_timed(engine, vocab, PREFILL_TOKENS, repeats=max(1, min(args.steps, 3)))
-                print(f"prefill {PREFILL_TOKENS} layers{args.layers}: {ms:.3f} ms")
+                tokens = max(2, min(args.prompt_tokens, 8192))
+                ms, _ = prefill_timed(engine, vocab, tokens, repeats=max(1, min(args.steps, 3)))
+                print(f"prefill {tokens} layers{args.layers}: {ms:.3f} ms")
             clocks.stop()
             return 0
         engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=64,
