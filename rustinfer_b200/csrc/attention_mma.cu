@@ -473,8 +473,8 @@ decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, 
 // ============================================================ decode, keys and values by TMA
 // The same arithmetic as decode_kernel (a warp takes 16 keys of every 64-key tile, mma.sync,
 // fp32 online softmax, the warps' states merged at the end), but no thread computes an address
-// in the cache: a fifth warp's one thread issues a TMA box per page and kv head into a ring of
-// 128-byte-swizzled stages (full/empty mbarriers), and the warps read them with ldmatrix
+// in the cache: a fifth warp issues a TMA box per page and kv head (each box from a lane of its
+// own) into a ring of 128-byte-swizzled stages (full/empty mbarriers), and the warps read them with ldmatrix
 // through the swizzle.  The cp.async kernel above spends its issue slots on page look-ups and
 // address arithmetic (3.4 TB/s at batch 8, 4.5 at batch 64); this one is bound by the ring.
 // Head sizes 64 and 128, pages of 8, 16, 32 or a multiple of 64 keys.
@@ -574,54 +574,55 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
         }
     }
     // ------------------------------------------------------------------------ TMA producer
-    // One thread, lean on purpose (it paces the CTA): no division in the loop, page numbers
-    // read one tile ahead.  Pages past the request's last one are never allocated: its first
-    // page is read instead (those keys are masked, their V rows zeroed before use).  Its first
-    // tiles go out before the other warps have q.
-    const bool producer = tid == DWARPS * 32;
+    // The fifth warp.  Lane 0 waits for a free stage and announces the bytes; every box of the tile
+    // (a page's keys or values, one 64-column block) goes out from a lane of its own, since one
+    // thread sends a box only every 74 ns and 8 to 16 boxes a tile from one thread paced the CTA.
+    // No division in the loop, page numbers read one tile ahead.  Pages past the request's last
+    // one are never allocated: its first page is read instead (those keys are masked, their V rows
+    // zeroed before use).  The first tiles go out before the other warps have q.
+    const bool producer = warp == DWARPS;
     const int* bt = block_table + (size_t)b * table_stride;
     const int boxes = DKT / box_rows;                      // at most 8 pages meet a tile
     const bool small_pages = page_size < DKT;
     const int kv_step = Hkv * page_size;
     const int t_newest = t_first + t_count - 1;            // the tile with this step's key
     int blk = (t_begin * DKT) / page_size, off = small_pages ? 0 : (t_begin * DKT) % page_size;
-    int pages[8], pages_next[8];
-    auto look_up = [&](int key0, int blk0, bool live, int (&dst)[8]) {
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-            dst[c] = (live && c < boxes) ? bt[key0 + c * box_rows < kvl ? blk0 + c : 0] : 0;
+    // this lane's box of a tile: keys or values, page p_c of the tile, 64-column block p_kb
+    const int p_kv = lane / (boxes * TKB), p_rem = lane - p_kv * boxes * TKB;
+    const int p_c = p_rem / TKB, p_kb = p_rem - p_c * TKB;
+    const bool p_mine = producer && lane < 2 * boxes * TKB;
+    auto look_up = [&](int key0, int blk0, bool live) -> int {
+        return (live && p_mine) ? bt[key0 + p_c * box_rows < kvl ? blk0 + p_c : 0] : 0;
     };
+    int page = 0;
     bool p_ok = true, waited = false;
     int p_s = 0;
     unsigned p_par = 1;
-    auto issue = [&](int t) {
+    auto issue = [&](int t) {                              // the whole producer warp
         const int key0 = t * DKT;
         int blk_n = blk, off_n = off;
         if (small_pages) blk_n += boxes;
         else if ((off_n += DKT) >= page_size) { off_n = 0; ++blk_n; }
-        look_up(key0 + DKT, blk_n, t + 1 < t_end, pages_next);
-        if (t - t_begin >= TSTAGES && !tbar_try_wait(&empty[p_s], p_par) && !tbar_wait(&empty[p_s], p_par, error)) { p_ok = false; return; }
+        const int page_next = look_up(key0 + DKT, blk_n, t + 1 < t_end);
+        int good = 1;
+        if (lane == 0 && t - t_begin >= TSTAGES && !tbar_try_wait(&empty[p_s], p_par) && !tbar_wait(&empty[p_s], p_par, error)) good = 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) { p_ok = false; return; }
         if (t >= t_newest && !waited) { pdl_wait(); waited = true; }
         unsigned char* dst = ring + (size_t)p_s * T_STAGE_BYTES;
-        tbar_expect_tx(&full[p_s], T_STAGE_BYTES);
-#pragma unroll
-        for (int kv = 0; kv < 2; ++kv)
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-                if (c < boxes) {
-                    const int row = (pages[c] * 2 * Hkv + kvh) * page_size + kv * kv_step + (key0 + c * box_rows < kvl ? off : 0);
-#pragma unroll
-                    for (int kb = 0; kb < TKB; ++kb)
-                        t_tma_load_2d(dst + kv * T_TILE_BYTES + kb * (DKT * 128) + c * box_rows * 128, &cache_map, &full[p_s], kb * 64, row);
-                }
-#pragma unroll
-        for (int c = 0; c < 8; ++c) pages[c] = pages_next[c];
+        if (lane == 0) tbar_expect_tx(&full[p_s], T_STAGE_BYTES);
+        if (p_mine) {
+            const int row = (page * 2 * Hkv + kvh) * page_size + p_kv * kv_step + (key0 + p_c * box_rows < kvl ? off : 0);
+            t_tma_load_2d(dst + p_kv * T_TILE_BYTES + p_kb * (DKT * 128) + p_c * box_rows * 128, &cache_map, &full[p_s], p_kb * 64, row);
+        }
+        page = page_next;
         blk = blk_n; off = off_n;
         if (++p_s == TSTAGES) { p_s = 0; p_par ^= 1u; }
     };
     const int t_early = min(t_end, t_begin + TSTAGES);
     if (producer) {
-        look_up(t_begin * DKT, blk, t_begin < t_end, pages);
+        __syncwarp();                                      // lane 0 has set the barriers up
+        page = look_up(t_begin * DKT, blk, t_begin < t_end);
         for (int t = t_begin; t < t_early && p_ok; ++t) issue(t);
     }
     __syncwarp();
@@ -633,8 +634,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap cache_map, const bf16* __r
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     if (warp == DWARPS) {
-        if (producer)
-            for (int t = t_early; t < t_end && p_ok; ++t) issue(t);
+        for (int t = t_early; t < t_end && p_ok; ++t) issue(t);
     } else {
         // ---------------------------------------------------------------------- the warps
         unsigned qf[KS][4];
