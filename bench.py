@@ -554,13 +554,23 @@ def main() -> int:
                 windows.append(w)
                 points[f"e2e_b{b}"] = round(b / ms_e * 1e3, 1)
                 say(f"decode b{b}: {ms_b:.4f} ms/step, e2e {ms_e:.4f}")
-            # the same steps with every token drawn (temperature 0.8, top-k 50, top-p 0.9) instead of the argmax
+            # the same steps with every token drawn (temperature 0.8, top-k 50, top-p 0.9) instead of the
+            # argmax.  Windows of the two kinds alternate and each drawn one is set against the greedy
+            # one before it: minutes into a run the clocks under the power cap move a window by
+            # several per cent, more than the sampler costs.
             sp = SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=1, max_tokens=CONTEXT, ignore_eos=True)
-            (ms_s, _, w), _all = median_of(
-                lambda: decode_device_timed(engine, args.batch, k, args.warmup, vocab, next(seeds), sampling=sp), 3)
-            windows.append(w)
+            drawn, ratios = [], []
+            for _ in range(3):
+                ms_g, _, w = decode_device_timed(engine, args.batch, k, args.warmup, vocab, next(seeds))
+                windows.append(w)
+                ms_s, _, w = decode_device_timed(engine, args.batch, k, args.warmup, vocab, next(seeds), sampling=sp)
+                windows.append(w)
+                drawn.append(ms_s)
+                ratios.append(ms_g / ms_s)
+            ms_s = statistics.median(drawn)
             points[f"decode_b{args.batch}_sampled"] = round(args.batch / ms_s * 1e3, 1)
-            say(f"decode b{args.batch} sampled: {ms_s:.4f} ms/step")
+            points[f"decode_b{args.batch}_sampled_vs_greedy"] = round(statistics.median(ratios), 4)
+            say(f"decode b{args.batch} sampled: {ms_s:.4f} ms/step, {statistics.median(ratios):.3f} of greedy windows beside it")
         del engine
         torch.cuda.empty_cache()
     if not args.skip_points and args.shape == "1b":

@@ -387,13 +387,15 @@ sample_select_kernel(const float* __restrict__ logits, int ld, int vocab, const 
     if (tid == 0) { x_nmp = n_mp; x_wmp = w_mp; s_cmd = -2; }
     cluster.sync();
 
-    // gather this CTA's tokens of bucket b into the first CTA's list
-    auto gather = [&](int b) {
+    // gather this CTA's tokens of the buckets lo..hi (a command is lo + hi * 65536) into the first CTA's list
+    auto gather = [&](int cmd) {
+        const int b_lo = cmd & 0xffff, b_hi = cmd >> 16;
         unsigned long long* far_list = cluster.map_shared_rank(list, 0);
         int* far_listed = cluster.map_shared_rank(&s_listed, 0);
         for_each_logit(row, begin, end, [&](int i, float raw) {
             const float v = clean(raw);
-            if (bucket_of(v, top, inv_t, per_unit) == b) {
+            const int bk = bucket_of(v, top, inv_t, per_unit);
+            if (bk >= b_lo && bk <= b_hi) {
                 const int at = atomicAdd(far_listed, 1);
                 if (at < CAP) far_list[at] = ((unsigned long long)ordered_bits(v) << 32) | (unsigned int)(0xffffffffu - (unsigned int)i);
             }
@@ -422,27 +424,38 @@ sample_select_kernel(const float* __restrict__ logits, int ld, int vocab, const 
     n_mp = 0ull; w_mp = 0ull;
     for (unsigned k = 0; k < CL; ++k) { n_mp += *cluster.map_shared_rank(&x_nmp, k); w_mp += *cluster.map_shared_rank(&x_wmp, k); }
     __syncthreads();
-    if (tid < 32) {
-        constexpr int PER = SB / 32;
-        unsigned int c = 0u;
-        unsigned long long w = 0ull;
-        for (int i = 0; i < PER; ++i) { c += cnt[tid * PER + i]; w += wsum[tid * PER + i]; }
-        unsigned int c_before = c;
-        unsigned long long w_before = w;
+    {
+        // counts and weights before each bucket: two buckets a thread, a scan over the warp, then over the warps
+        static_assert(SB == 2 * ST, "two buckets a thread");
+        const unsigned int c0 = cnt[2 * tid], c1 = cnt[2 * tid + 1];
+        const unsigned long long w0 = wsum[2 * tid], w1 = wsum[2 * tid + 1];
+        unsigned int c_incl = c0 + c1;
+        unsigned long long w_incl = w0 + w1;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const unsigned int ct = __shfl_up_sync(0xffffffffu, c_before, o);
-            const unsigned long long wt = __shfl_up_sync(0xffffffffu, w_before, o);
-            if (tid >= o) { c_before += ct; w_before += wt; }
+            const unsigned int ct = __shfl_up_sync(0xffffffffu, c_incl, o);
+            const unsigned long long wt = __shfl_up_sync(0xffffffffu, w_incl, o);
+            if ((tid & 31) >= o) { c_incl += ct; w_incl += wt; }
         }
-        c_before -= c; w_before -= w;
-        for (int i = 0; i < PER; ++i) {
-            const unsigned int ci = cnt[tid * PER + i];
-            const unsigned long long wi = wsum[tid * PER + i];
-            cnt[tid * PER + i] = c_before; wsum[tid * PER + i] = w_before;
-            c_before += ci; w_before += wi;
+        __syncthreads();                                   // every thread has read its buckets and `red` is free
+        if ((tid & 31) == 31) { red[tid >> 5] = w_incl; red[32 + (tid >> 5)] = c_incl; }
+        __syncthreads();
+        if (tid < 32) {
+            unsigned long long wt = red[tid], wi = wt;
+            unsigned long long ct = red[32 + tid], ci = ct;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long a = __shfl_up_sync(0xffffffffu, wi, o), c = __shfl_up_sync(0xffffffffu, ci, o);
+                if (tid >= o) { wi += a; ci += c; }
+            }
+            red[tid] = wi - wt; red[32 + tid] = ci - ct;    // what lies before each warp
+            if (tid == 31) wsum[SB] = wi;
         }
-        if (tid == 31) wsum[SB] = w_before;
+        __syncthreads();
+        const unsigned int c_before = (unsigned int)red[32 + (tid >> 5)] + c_incl - (c0 + c1);
+        const unsigned long long w_before = red[tid >> 5] + w_incl - (w0 + w1);
+        cnt[2 * tid] = c_before; cnt[2 * tid + 1] = c_before + c0;
+        wsum[2 * tid] = w_before; wsum[2 * tid + 1] = w_before + w0;
     }
     __syncthreads();
     const unsigned long long total_all = wsum[SB];
@@ -453,19 +466,21 @@ sample_select_kernel(const float* __restrict__ logits, int ld, int vocab, const 
         while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if ((int)cnt[mid] <= rk) lo = mid; else hi = mid - 1; }
         return lo;
     };
-    int cur = -1, cur_n = 0;                              // the bucket in the list, sorted, with its running weights
-    // bucket b's tokens, sorted (largest logit first, lowest id among equals), and the running weight over
-    // them; false: too many for the list
-    auto load_bucket = [&](int b) -> bool {
-        if (cur == b) return true;
-        const int n = count_of(b);
+    // The list holds the tokens of the buckets cur_lo..cur_hi, sorted (largest logit first, lowest id
+    // among equals), with the running weight over them; base_c tokens of weight base_w lie before them.
+    int cur_lo = -1, cur_hi = -2, cur_n = 0, base_c = 0;
+    unsigned long long base_w = 0ull;
+    // buckets lo..hi into the list; false: too many tokens for it
+    auto load_range = [&](int lo, int hi) -> bool {
+        if (lo >= cur_lo && hi <= cur_hi) return true;
+        const int n = (int)((hi + 1 < SB ? cnt[hi + 1] : (unsigned int)vocab) - cnt[lo]);
         if (n > CAP) return false;
         int pad = 1;
         while (pad < n) pad <<= 1;
         for (int i = tid; i < pad; i += ST) list[i] = 0ull;
-        if (tid == 0) { s_listed = 0; s_cmd = b; }
+        if (tid == 0) { s_listed = 0; s_cmd = lo | (hi << 16); }
         cluster.sync();                                    // the command is there (and the list is clear)
-        gather(b);
+        gather(lo | (hi << 16));
         cluster.sync();                                    // the list is complete
         for (int k = 2; k <= pad; k <<= 1)
             for (int j = k >> 1; j > 0; j >>= 1) {
@@ -512,16 +527,25 @@ sample_select_kernel(const float* __restrict__ logits, int ld, int vocab, const 
             if (4 * tid + e < CAP) cum[4 * tid + e] = run;
         }
         __syncthreads();
-        cur = b; cur_n = n;
+        cur_lo = lo; cur_hi = hi; cur_n = n; base_c = (int)cnt[lo]; base_w = wsum[lo];
         return true;
     };
-    // the first token j of the loaded bucket (its rank below `limit`) for which pred(running weight) holds;
+    // One bucket.  `more`: something is asked after this, and it lies in this bucket or an earlier one
+    // (the top-k cut bounds the top-p prefix, and that the draw): where the buckets from the first one
+    // up to this one hold no more than a thousand tokens, all of them are listed at once, one pass over
+    // the row and one sort instead of up to three.
+    auto load_bucket = [&](int b, bool more) -> bool {
+        if (b >= cur_lo && b <= cur_hi) return true;
+        if (more && (b + 1 < SB ? cnt[b + 1] : (unsigned int)vocab) <= 1024u) return load_range(0, b);
+        return load_range(b, b);
+    };
+    // the first token j of the list (its rank below `limit`) for which pred(running weight) holds;
     // -1 if none
-    auto first_where = [&](int b, int limit, auto pred) -> int {
+    auto first_where = [&](int limit, auto pred) -> int {
         if (tid == 0) s_found = 0x7fffffff;
         __syncthreads();
         for (int j = tid; j < cur_n; j += ST)
-            if ((int)cnt[b] + j < limit && pred(wsum[b] + cum[j])) { atomicMin(&s_found, j); break; }
+            if (base_c + j < limit && pred(base_w + cum[j])) { atomicMin(&s_found, j); break; }
         __syncthreads();
         const int j = s_found;
         __syncthreads();
@@ -539,9 +563,9 @@ sample_select_kernel(const float* __restrict__ logits, int ld, int vocab, const 
         total = w_mp;
     } else if (K < vocab) {
         const int b = bucket_of_rank(K - 1);
-        fine = load_bucket(b);
+        fine = load_bucket(b, true);
         kept = K;
-        total = fine ? wsum[b] + cum[K - 1 - (int)cnt[b]] : 0ull;
+        total = fine ? base_w + cum[K - 1 - base_c] : 0ull;
     } else {
         kept = vocab;
         total = total_all;
@@ -552,10 +576,10 @@ sample_select_kernel(const float* __restrict__ logits, int ld, int vocab, const 
         const double need = (double)tp * (double)total;
         int lo = 0, hi = SB - 1;                           // the first bucket at whose end the running weight has reached `need`
         while (lo < hi) { const int mid = (lo + hi) >> 1; if ((double)wsum[mid + 1] >= need) hi = mid; else lo = mid + 1; }
-        fine = load_bucket(lo);
+        fine = load_bucket(lo, true);
         if (fine) {
-            const int j = first_where(lo, kept, [&](unsigned long long c) { return (double)c >= need; });
-            if (j >= 0) { kept = (int)cnt[lo] + j + 1; final_total = wsum[lo] + cum[j]; }
+            const int j = first_where(kept, [&](unsigned long long c) { return (double)c >= need; });
+            if (j >= 0) { kept = base_c + j + 1; final_total = base_w + cum[j]; }
         }
     }
     // ---- the draw: the first token at which the running weight passes u * final_total
@@ -567,10 +591,10 @@ sample_select_kernel(const float* __restrict__ logits, int ld, int vocab, const 
         while (lo < hi) { const int mid = (lo + hi) >> 1; if ((double)wsum[mid + 1] > target) hi = mid; else lo = mid + 1; }
         int b = lo;
         if ((int)cnt[b] >= kept) b = bucket_of_rank(kept - 1);     // the target lies past the kept prefix: its last token
-        fine = load_bucket(b);
+        fine = load_bucket(b, false);
         if (fine) {
-            int j = first_where(b, kept, [&](unsigned long long c) { return target < (double)c; });
-            if (j < 0) j = min(cur_n, kept - (int)cnt[b]) - 1;     // never passed inside the prefix: its last token here
+            int j = first_where(kept, [&](unsigned long long c) { return target < (double)c; });
+            if (j < 0) j = min(cur_n, kept - base_c) - 1;          // never passed inside the prefix: its last token here
             if (j >= 0) token = (int)(0xffffffffu - (unsigned int)(list[j] & 0xffffffffu));
             else fine = false;
         }
