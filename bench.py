@@ -544,7 +544,7 @@ def main() -> int:
         points = {}
         if not args.skip_points:
             from rustinfer_b200.sampling.params import SamplingParams
-            k = min(args.steps, 64)
+            k = args.steps
             for b in (1, 64):
                 (ms_b, _, w), _all = median_of(lambda: decode_device_timed(engine, b, k, args.warmup, vocab, next(seeds)), 3)
                 windows.append(w)
@@ -638,7 +638,9 @@ def further_shapes(args, hbm_gbs, bf16_tflops, windows, say):
     from rustinfer_b200.weights.random_init import write_random_model
     out = {}
     seeds = iter(range(20_000, 30_000))
-    k = min(args.steps, 32)
+    # (windows as long as the headline's: the steps right after the burst that fills the context run
+    # several per cent slower than the ones that follow, and a short window is mostly those)
+    k = args.steps
     # ---- Llama-3.1-8B-shaped, 8 of 32 layers
     name, shape = SHAPES["8b"]
     layers = 8
