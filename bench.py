@@ -471,6 +471,8 @@ def main() -> int:
                          "serve: 64 requests, prompts of 128 to 2,048 tokens, 256 tokens out each, "
                          "prompt portions of 512, through Engine.generate")
     ap.add_argument("--eager", action="store_true", help="with --only decode: no CUDA graphs")
+    ap.add_argument("--sampled", action="store_true",
+                    help="with --only decode: every token drawn (temperature 0.8, top-k 50, top-p 0.9) instead of the argmax")
     ap.add_argument("--context", type=int, default=CONTEXT, help="with --only: context the decode ends at")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only prefill: length of the prompt, computed in one step (up to 8192)")
@@ -514,8 +516,12 @@ def main() -> int:
                             capture_sizes=[] if args.eager else [1, 2, 4, 8, 16, 32, 64], ignore_eos=True)
             if args.only == "decode":
                 global_ctx = args.context
-                ms, n, _ = decode_device_timed(engine, args.batch, args.steps, args.warmup, vocab, 1, global_ctx)
-                print(f"decode b{args.batch} ctx{global_ctx} layers{args.layers}: {ms:.4f} ms/step, {n} launches")
+                sp = None
+                if args.sampled:
+                    from rustinfer_b200.sampling.params import SamplingParams
+                    sp = SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=1, max_tokens=CONTEXT, ignore_eos=True)
+                ms, n, _ = decode_device_timed(engine, args.batch, args.steps, args.warmup, vocab, 1, global_ctx, sampling=sp)
+                print(f"decode b{args.batch} ctx{global_ctx} layers{args.layers}{' sampled' if sp else ''}: {ms:.4f} ms/step, {n} launches")
             else:
                 tokens = max(2, min(args.prompt_tokens, 8192))
                 ms, _ = prefill_timed(engine, vocab, tokens, repeats=max(1, min(args.steps, 3)))
