@@ -36,7 +36,7 @@ constexpr int BM = 128;                 // rows of the A operand per tile (MMA M
 constexpr int BK = 64;                  // 64 bf16 = one 128-byte swizzle row
 constexpr int THREADS = 192;
 
-enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_RESIDUAL = 3 };
+enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2, EPI_RESIDUAL = 3, EPI_ROPE = 4 };
 enum ErrorCode { ERR_PRODUCER_WAIT = 1, ERR_MMA_WAIT = 2, ERR_EPILOGUE_WAIT = 3, ERR_DRAIN_WAIT = 4 };
 
 
@@ -82,6 +82,14 @@ struct Params {
     int sk_tiles;                        // tiles dealt out that way (0: none), the last of n_tiles
     int sk_pairs, sk_q, sk_extra;        // pairs that take part; k-blocks of each: sk_q, the first sk_extra one more
     float* sk_acc;                       // [pair][first or second tile of its run][2 CTAs][4 warps][width/4][32 lanes][4] fp32
+    // EPI_ROPE (CTA pairs only): the product is q, k, v of many tokens; q and k heads are rotated
+    // straight from the accumulator, q goes to `out` (bf16 [tokens][ld_out]), k and v into their pages
+    const int* rope_positions;           // [tokens]
+    const float* rope_cos;               // [positions][head_dim / 2]
+    const float* rope_sin;
+    const int* rope_slot;                // [tokens] slot of the token's key in the cache, < 0: none; null: no keys
+    bf16* rope_cache;                    // [page][K|V][kv head][slot][head_dim]
+    int rope_hq, rope_hkv, rope_hd, rope_page;
 };
 
 
@@ -510,6 +518,92 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t* bar, unsigned rank)
                  ::"r"(smem_u32(bar)), "r"(rank) : "memory");
 }
 
+// The rotary epilogue of one warp's 32 token rows of a tile, columns [b0, b0 + width): whole heads
+// (the width and b0 are multiples of the head size).  A thread owns a token's row; the halves of a
+// head that the rotation pairs up, (i, i + head_dim / 2), both lie in its accumulator row.  32
+// columns of each half at a time: RustInfer rotates q and k in place after the product has
+// rounded them to bf16 (crates/infer-backend-cuda/src/kernels/rope/rope.cu:107-132); here the fp32
+// accumulator is rotated and rounded once, as in the few-token chain.
+struct RopeRow {                    // what a thread needs of its token before the accumulator is there
+    bool live;
+    int slot;
+    const float* ct;
+    const float* st;
+    float c[32], s[32];             // cos and sin of the first 32 pairs of a head at the token's position
+};
+__device__ __forceinline__ void rope_row_begin(const Params& p, int tok, RopeRow& r) {
+    const int half = p.rope_hd >> 1;
+    r.live = tok < p.a_rows;
+    const int pos = r.live ? p.rope_positions[tok] : 0;
+    r.slot = (r.live && p.rope_slot) ? p.rope_slot[tok] : -1;
+    r.ct = p.rope_cos + (size_t)pos * half;
+    r.st = p.rope_sin + (size_t)pos * half;
+#pragma unroll
+    for (int k = 0; k < 32; k += 4) {
+        *reinterpret_cast<float4*>(r.c + k) = *reinterpret_cast<const float4*>(r.ct + k);
+        *reinterpret_cast<float4*>(r.s + k) = *reinterpret_cast<const float4*>(r.st + k);
+    }
+}
+__device__ __forceinline__ void rope_rows(const Params& p, unsigned taddr, int tok, int b0, int width, RopeRow& r) {
+    const int hd = p.rope_hd, half = hd >> 1;
+    const bool live = r.live;
+    bf16* kdst = nullptr;
+    bf16* vdst = nullptr;
+    if (r.slot >= 0) {
+        const int page = r.slot / p.rope_page, off = r.slot - page * p.rope_page;
+        kdst = p.rope_cache + ((size_t)(page * 2 + 0) * p.rope_hkv * p.rope_page + off) * hd;
+        vdst = p.rope_cache + ((size_t)(page * 2 + 1) * p.rope_hkv * p.rope_page + off) * hd;
+    }
+    const size_t head_step = (size_t)p.rope_page * hd;
+    bf16* qrow = reinterpret_cast<bf16*>(p.out) + (size_t)tok * p.ld_out;
+    // 32 pairs at a time over all heads of the tile: their cos and sin are the same for every head
+#pragma unroll 1
+    for (int i0 = 0; i0 < half; i0 += 32) {
+        if (i0 > 0) {
+#pragma unroll
+            for (int k = 0; k < 32; k += 4) {
+                *reinterpret_cast<float4*>(r.c + k) = *reinterpret_cast<const float4*>(r.ct + i0 + k);
+                *reinterpret_cast<float4*>(r.s + k) = *reinterpret_cast<const float4*>(r.st + i0 + k);
+            }
+        }
+#pragma unroll 1
+        for (int c0 = 0; c0 < width && b0 + c0 < p.b_rows; c0 += hd) {
+            const int head = (b0 + c0) / hd;
+            if (head < p.rope_hq + p.rope_hkv) {
+                bf16* dst = head < p.rope_hq ? qrow + (size_t)head * hd
+                                             : (kdst ? kdst + (size_t)(head - p.rope_hq) * head_step : nullptr);
+                float lo[32], hi[32];
+                tmem_ld_row<32>(taddr + c0 + i0, lo);                 // every lane of the warp takes part
+                tmem_ld_row<32>(taddr + c0 + half + i0, hi);
+                if (live && dst) {
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) {
+                        const float y1 = lo[k] * r.c[k] - hi[k] * r.s[k];
+                        hi[k] = lo[k] * r.s[k] + hi[k] * r.c[k];
+                        lo[k] = y1;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 32; k += 8) {
+                        *reinterpret_cast<uint4*>(dst + i0 + k) = pack8(lo + k);
+                        *reinterpret_cast<uint4*>(dst + half + i0 + k) = pack8(hi + k);
+                    }
+                }
+            } else if (i0 == 0) {
+                bf16* dst = vdst ? vdst + (size_t)(head - p.rope_hq - p.rope_hkv) * head_step : nullptr;
+#pragma unroll 1
+                for (int j0 = 0; j0 < hd; j0 += 32) {
+                    float v[32];
+                    tmem_ld_row<32>(taddr + c0 + j0, v);
+                    if (live && dst) {
+#pragma unroll
+                        for (int k = 0; k < 32; k += 8) *reinterpret_cast<uint4*>(dst + j0 + k) = pack8(v + k);
+                    }
+                }
+            }
+        }
+    }
+}
+
 // What a pair works on next: a whole tile, or a run of k-blocks of one of the dealt-out tiles.
 struct PairItem { int tile, kb0, kb1, part; };
 // first k-block (counted through the dealt-out tiles) of a pair's run
@@ -644,6 +738,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int a0 = (tile % p.tiles_a) * 256 + (int)rank * BM, b0 = (tile / p.tiles_a) * BN;
             const int ra = a0 + quarter * 32 + lane;
             const int buf = t & 1, use = t >> 1;
+            RopeRow rr;
+            if (p.epilogue == EPI_ROPE) rope_row_begin(p, ra, rr);      // the table's rows come while the tile is computed
             if (ok) ok = mbar_wait(&acc_full[buf], use & 1, p.error, ERR_EPILOGUE_WAIT);
             tc_fence_after();
             const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + buf * ACC_COLS;
@@ -691,7 +787,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     if (lane == 0) p.counters[slot] = 0;
                 }
             }
-            if (finish) {
+            if (finish && p.epilogue == EPI_ROPE) {
+                rope_rows(p, taddr, ra, b0, BN, rr);
+            } else if (finish) {
                 // 64 columns a round trip to tensor memory where the tile lies inside the matrix:
                 // the epilogue of a pair's last tile has no MMA to hide behind.  At the ragged
                 // edge 16 at a time, element by element.
@@ -807,9 +905,10 @@ RI_API void ri_gemm_tc_set_stream_budget(int bytes) {
 // fewer than 128 evens out the last wave of tiles over the SMs).
 // sk_acc: SMs x 65536 floats where the parts of tiles that several CTA pairs share meet (two
 // 256 x 256 fp32 tiles a pair); null: every tile stays with one pair.
-RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* out, int ld_out, int epilogue,
-                      int swap, int bn, int splits, int a_box, float* workspace, int* counters, int* error,
-                      float* sk_acc, void* stream) {
+namespace {
+int gemm_tc_impl(const void* X, const void* W, int M, int N, int K, void* out, int ld_out, int epilogue,
+                 int swap, int bn, int splits, int a_box, float* workspace, int* counters, int* error,
+                 float* sk_acc, const Params* rope, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || splits < 1 || (splits > 1 && (!workspace || !counters)) || !error ||
         a_box < 8 || a_box > BM || a_box % 8 != 0)
@@ -819,6 +918,14 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
     Params p;
     p.pair_bn = 0;
     p.sk_tiles = p.sk_pairs = p.sk_q = p.sk_extra = 0; p.sk_acc = nullptr;
+    p.rope_positions = nullptr; p.rope_cos = p.rope_sin = nullptr; p.rope_slot = nullptr; p.rope_cache = nullptr;
+    p.rope_hq = p.rope_hkv = p.rope_hd = p.rope_page = 0;
+    if (rope) {
+        p.rope_positions = rope->rope_positions; p.rope_cos = rope->rope_cos; p.rope_sin = rope->rope_sin;
+        p.rope_slot = rope->rope_slot; p.rope_cache = rope->rope_cache;
+        p.rope_hq = rope->rope_hq; p.rope_hkv = rope->rope_hkv; p.rope_hd = rope->rope_hd; p.rope_page = rope->rope_page;
+        sk_acc = nullptr;                                  // whole heads stay with one pair
+    }
     p.a_rows = swap ? N : M;
     p.b_rows = swap ? M : N;
     p.K = K; p.swap = swap; p.epilogue = epilogue; p.out = out; p.ld_out = ld_out; p.splits = splits;
@@ -865,6 +972,7 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
         if (deal_off) sk_acc = nullptr;
         long long best = -1;
         for (int w : {256, 192}) {
+            if (rope && w % p.rope_hd != 0) continue;      // a tile holds whole heads
             const int tiles = p.tiles_a * ((p.b_rows + w - 1) / w);
             const int waves = tiles / pairs, rest = tiles % pairs;
             for (int deal = 0; deal < 2; ++deal) {
@@ -899,6 +1007,7 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
         if (stp != 0) return stp;
         return launch_pair(ma, mb, p, (cudaStream_t)stream);
     }
+    if (rope) return (int)cudaErrorNotSupported;           // only the CTA-pair kernel has that epilogue
     int st = make_map(A, p.a_rows, K, a_box, &ma);
     if (st != 0) return st;
     st = make_map(B, p.b_rows, K, bn, &mb);
@@ -913,4 +1022,38 @@ RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* o
         case 256: return launch<256>(ma, mb, p, tiles, s);
     }
     return (int)cudaErrorInvalidValue;
+}
+}  // namespace
+
+RI_API int ri_gemm_tc(const void* X, const void* W, int M, int N, int K, void* out, int ld_out, int epilogue,
+                      int swap, int bn, int splits, int a_box, float* workspace, int* counters, int* error,
+                      float* sk_acc, void* stream) {
+    if (epilogue == EPI_ROPE) return (int)cudaErrorInvalidValue;       // has an entry of its own
+    return gemm_tc_impl(X, W, M, N, K, out, ld_out, epilogue, swap, bn, splits, a_box, workspace, counters, error,
+                        sk_acc, nullptr, stream);
+}
+
+// q, k, v of many tokens with the rotary encoding and the cache write in the product's epilogue
+// (CTA pairs: 512 tokens or more).  X [M][K] bf16, W [N][K] bf16 with N = (Hq + 2 Hkv) head_dim
+// rows, or Hq head_dim when the layer keeps no keys (slot_of_token and cache null, Hkv 0).  q_out
+// bf16 [M][ld_q] gets the rotated q heads; k (rotated) and v go to the token's slot of the cache
+// [page][K|V][kv head][slot][head_dim] (slot < 0: not written).  cos, sin: fp32 [positions][head_dim / 2].
+// Head sizes 64 and 128, the whole head rotated.  cudaErrorNotSupported (801) where the pair kernel does
+// not take the product: the caller then runs the product and the rotary kernel one after the other.
+RI_API int ri_gemm_tc_rope(const void* X, const void* W, int M, int N, int K, void* q_out, int ld_q,
+                           const int* positions, const float* cos_t, const float* sin_t, const int* slot_of_token,
+                           void* cache, int Hq, int Hkv, int head_dim, int page_size, int* counters, int* error,
+                           void* stream) {
+    if (M <= 0) return 0;
+    if ((head_dim != 64 && head_dim != 128) || Hq <= 0 || Hkv < 0 || N != (Hq + 2 * Hkv) * head_dim || !positions ||
+        !cos_t || !sin_t || (Hkv > 0 && (!slot_of_token || !cache || page_size <= 0)) || ld_q % 8 != 0 ||
+        (reinterpret_cast<uintptr_t>(q_out) & 15) || (reinterpret_cast<uintptr_t>(cache) & 15) ||
+        (reinterpret_cast<uintptr_t>(cos_t) & 15) || (reinterpret_cast<uintptr_t>(sin_t) & 15))
+        return (int)cudaErrorInvalidValue;
+    if (M < 512 || N < PAIR_BN) return (int)cudaErrorNotSupported;
+    Params r;
+    r.rope_positions = positions; r.rope_cos = cos_t; r.rope_sin = sin_t;
+    r.rope_slot = Hkv > 0 ? slot_of_token : nullptr; r.rope_cache = (bf16*)cache;
+    r.rope_hq = Hq; r.rope_hkv = Hkv; r.rope_hd = head_dim; r.rope_page = page_size;
+    return gemm_tc_impl(X, W, M, N, K, q_out, ld_q, EPI_ROPE, 0, PAIR_BN, 1, BM, nullptr, counters, error, nullptr, &r, stream);
 }

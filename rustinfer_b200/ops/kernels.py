@@ -214,6 +214,38 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int =
                                  a_box, _p(ws), _p(counters), _p(err), _p(meeting), stream_ptr()), "gemm_tc")
 
 
+def gemm_tc_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, positions: torch.Tensor,
+                 cos: torch.Tensor, sin: torch.Tensor, slot_of_token: Optional[torch.Tensor],
+                 cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """q, k, v = x[M,K] @ w[N,K]^T with the rotary encoding and the write of keys and values into
+    their pages in the product's epilogue: q_out [M, num_heads * head_dim] bf16 gets the rotated
+    queries.  `num_kv_heads` 0 (no slots, no cache) for a layer that keeps no keys.  False when the
+    kernel does not take the product (fewer than 512 tokens, another head size): nothing was
+    launched, and the caller runs the product and `rope_scatter` one after the other."""
+    require_cuda(x, w, q_out, positions, cos, sin)
+    M, Kd = x.shape
+    N = w.shape[0]
+    if (M < 512 or head_dim not in (64, 128) or not gemm_tc_supports(x, w) or cos.dtype != torch.float32
+            or cos.shape[-1] * 2 != head_dim or q_out.dtype != torch.bfloat16 or q_out.stride(1) != 1
+            or N != (num_heads + 2 * num_kv_heads) * head_dim or N < 256):
+        return False
+    page = 0
+    if num_kv_heads > 0:
+        if slot_of_token is None or cache is None:
+            raise KernelError("gemm_tc_rope: a layer with keys needs the tokens' slots and the cache")
+        require_cuda(slot_of_token, cache)
+        page = cache.shape[3]
+    _ws, counters, err, _meet = gemm_tc_state(x.device)
+    st = L.gemm_tc().ri_gemm_tc_rope(_p(x), _p(w), M, N, Kd, _p(q_out), q_out.stride(0), _p(positions), _p(cos), _p(sin),
+                                     _p(slot_of_token) if num_kv_heads > 0 else None,
+                                     _p(cache) if num_kv_heads > 0 else None, num_heads, num_kv_heads, head_dim,
+                                     page, _p(counters), _p(err), stream_ptr())
+    if st == 801:                                           # not supported for this product: nothing was launched
+        return False
+    check(st, "gemm_tc_rope")
+    return True
+
+
 class _ChainPhase(ctypes.Structure):
     _fields_ = [("w", ctypes.c_void_p), ("N", ctypes.c_int), ("K", ctypes.c_int), ("x_kind", ctypes.c_int),
                 ("ld_x", ctypes.c_int), ("x_rows", ctypes.c_int), ("x", ctypes.c_void_p), ("norm_w", ctypes.c_void_p),

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "ri_attention_prefill_tc": [_P, _I, _P, _I, _P, _L, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _P],
     "ri_attention_tc_supports": [_I, _I, _I],
     "ri_gemm_tc": [_P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
+    "ri_gemm_tc_rope": [_P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "ri_decode_chain": [_P, _I, _P, _I, _P, _P, _I, _P],
     "ri_decode_chain_fits": [_P, _I, _I, _I],
     "ri_attention_plain": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],

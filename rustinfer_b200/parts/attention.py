@@ -64,6 +64,9 @@ class GQAAttention(Mixer):
         # bf16 runs on the tensor-core kernels (head sizes up to 256); fp32, and larger heads,
         # on the plain fp32-arithmetic kernel
         self.use_mma = ctx.dtype == torch.bfloat16 and self.hd <= L.MMA_MAX_HEAD_DIM
+        # steps of 512 tokens or more: rotary encoding and cache write inside the q,k,v product
+        self.fuse_rope = (ctx.dtype == torch.bfloat16 and self.hd in (64, 128)
+                          and os.environ.get("RUSTINFER_B200_FUSE_ROPE", "1") != "0")
         # prompt portions: the tcgen05 kernel where it takes the geometry, else the mma.sync one
         self.use_tc = (self.use_mma and os.environ.get("RUSTINFER_B200_PREFILL_ATTENTION", "tc") != "mma"
                        and K.tc_attention_supports(self.Hq, self.Hkv, self.hd, ctx.page_size))
@@ -117,8 +120,17 @@ class GQAAttention(Mixer):
                 residual: Optional[torch.Tensor] = None):
         """Returns the sublayer's output, or None when it was added into `residual`."""
         g = step.groups[cache.group]
-        qkv = self.qkv(x, out_dtype=self.ctx.dtype)
         writes = self.own_kv and cache.writes
+        # many tokens: the product rotates q and k and writes keys and values into their pages in
+        # its own epilogue (no pass over q, k, v in between)
+        if (self.fuse_rope and self.position is not None and self.position.rotary_dim == self.hd
+                and x.shape[0] >= 512 and (writes or not self.own_kv) and self.qkv.tensor_core):
+            q = torch.empty((x.shape[0], self.Hq * self.hd), dtype=torch.bfloat16, device=x.device)
+            if K.gemm_tc_rope(x, self.qkv.weight, q, step.positions, self.position.cos, self.position.sin,
+                              g.slot_of_token if writes else None, cache.kv if writes else None,
+                              self.Hq, self.Hkv if writes else 0, self.hd):
+                return self._project_out(self.attend(q, step, cache), residual)
+        qkv = self.qkv(x, out_dtype=self.ctx.dtype)
         if self.position is not None:
             # a layer that reads another's cache has only the q projection: qkv is q alone
             K.rope_scatter(qkv, step.positions, self.position.cos,

@@ -280,6 +280,55 @@ def test_rope_scatter(dt, Hq, Hkv, hd, rot, page):
     assert torch.equal(cache.double().cpu()[untouched], want[untouched])
 
 
+@pytest.mark.parametrize("M,hidden,Hq,Hkv,hd,page", [
+    (600, 136, 8, 2, 64, 16),                    # a ragged last row tile, three tiles of 256 columns
+    (1030, 264, 6, 2, 128, 8),                   # heads of 128: a tile holds two heads
+    (512, 72, 5, 0, 64, 16),                     # a layer that keeps no keys: q alone
+    (700, 200, 24, 8, 128, 32),                  # the 3B grouping, many column tiles
+])
+def test_gemm_tc_with_rotary_epilogue(M, hidden, Hq, Hkv, hd, page):
+    """q, k, v of many tokens with the rotary encoding and the cache write in the product's
+    epilogue, against the float64 product rotated by the plain implementation; tokens without a
+    slot are not stored and no other slot of the cache is touched."""
+    torch.manual_seed(M + hd)
+    k = K()
+    N = (Hq + 2 * Hkv) * hd
+    maxpos, pages = 300, (M + page - 1) // page + 3
+    x = torch.randn(M, hidden).bfloat16()
+    w = (torch.randn(N, hidden) / math.sqrt(hidden)).bfloat16()
+    pos = torch.randint(0, maxpos, (M,), dtype=torch.int32)
+    c, s_ = _rope_tables(maxpos, hd)
+    slots = torch.randperm(pages * page)[:M].to(torch.int32)
+    slots[7] = -1
+    cache = torch.full((pages, 2, max(Hkv, 1), page, hd), 7.0, dtype=BF, device=dev()) if Hkv else None
+    q = torch.full((M, Hq * hd), float("nan"), dtype=BF, device=dev())
+    ran = k.gemm_tc_rope(x.to(dev()), w.to(dev()), q, pos.to(dev()), c.float().to(dev()), s_.float().to(dev()),
+                         slots.to(dev()) if Hkv else None, cache, Hq, Hkv, hd)
+    assert ran
+    torch.cuda.synchronize()
+    assert k.gemm_tc_error(dev()) == 0
+    y = (x.double() @ w.double().T).view(M, Hq + 2 * Hkv, hd)
+    f = P.rope_inv_freq(hd, 10000.0, None)
+    rotated = P.rope_rotate(y[:, : Hq + Hkv], pos, f)
+    close(q.double().cpu().view(M, Hq, hd), rotated[:, :Hq], BF)
+    if Hkv:
+        want = torch.full((pages, 2, Hkv, page, hd), 7.0, dtype=torch.float64)
+        for t in range(M):
+            if slots[t] < 0:
+                continue
+            pg, off = int(slots[t]) // page, int(slots[t]) % page
+            want[pg, 0, :, off] = rotated[t, Hq:]
+            want[pg, 1, :, off] = y[t, Hq + Hkv:]
+        close(cache, want, BF, scale=float(y.abs().max()))
+        untouched = want == 7.0
+        assert torch.equal(cache.double().cpu()[untouched], want[untouched])
+    # fewer than 512 tokens: the caller is told to go the two-kernel way, and nothing is written
+    q2 = torch.full((100, Hq * hd), float("nan"), dtype=BF, device=dev())
+    assert not k.gemm_tc_rope(x[:100].contiguous().to(dev()), w.to(dev()), q2, pos[:100].to(dev()), c.float().to(dev()),
+                              s_.float().to(dev()), slots[:100].to(dev()) if Hkv else None, cache, Hq, Hkv, hd)
+    assert torch.isnan(q2.float()).all()
+
+
 @pytest.mark.parametrize("M,hidden,inter,Hq,Hkv,hd,rot,page", [
     (8, 2048, 8192, 32, 8, 64, 64, 16),          # the shapes of a 1B decoder
     (4, 4096, 14336, 32, 8, 128, 128, 16),        # ... of an 8B one: rows of the stream staged four at a time
