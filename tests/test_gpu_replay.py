@@ -84,6 +84,45 @@ def run_cuts(r, rid, ids, cuts):
     return torch.cat(outs)
 
 
+@pytest.mark.parametrize("name", FAST)
+def test_steps_of_many_tokens(models, name, monkeypatch):
+    """Steps of 512 tokens or more take the q,k,v product with the rotary encoding and the cache
+    write in its epilogue.  Every position of a 700-token prompt against the plain model; the same
+    prompt in portions of 520 + 180 and 690 + ten single tokens (which read the keys that epilogue
+    wrote); a second request's 600 tokens beside a decoded token of the first; and all of it again
+    with the rotary kernel run on its own: the two ways round q and k at different places, so they
+    differ by roundings, half the tolerance against the plain model at most (the bound the ways of
+    decoding are held to further down)."""
+    from rustinfer_b200.engine.runner import ModelRunner, StepEntry
+    folder, plain = models[name]
+    V = TINY[name]["vocab_size"]
+    ids = random_ids(700, V, 41)
+    other = random_ids(600, V, 42)
+    ref, ref_other = plain.logits(ids), plain.logits(other)
+    outs = {}
+    for fused in (True, False):
+        monkeypatch.setenv("RUSTINFER_B200_FUSE_ROPE", "1" if fused else "0")
+        r = ModelRunner(folder, dtype="bfloat16", max_model_len=1024, page_size=16, num_pages=2 * 64 + 4,
+                        max_batch_seqs=4, max_batch_tokens=1024)
+        assert r.model.blocks[0].mixer.fuse_rope == fused
+        whole = run_cuts(r, "w", ids, [700])
+        assert rel_err(whole, ref) <= TOL["bfloat16"]
+        assert rel_err(run_cuts(r, "p", ids, [520, 180]), ref) <= TOL["bfloat16"]
+        assert rel_err(run_cuts(r, "t", ids, [690] + [1] * 10), ref) <= TOL["bfloat16"]
+        # 600 prompt tokens of one request beside a decoded token of another in one step
+        r.open("a"); r.open("b")
+        r.step([StepEntry("a", ids[:650], [])])
+        lg = r.step([StepEntry("a", ids[650:651], [0]), StepEntry("b", other, list(range(600)))])
+        assert rel_err(lg[:1], ref[650:651]) <= TOL["bfloat16"]
+        assert rel_err(lg[1:], ref_other) <= TOL["bfloat16"]
+        r.close("a"); r.close("b")
+        torch.cuda.synchronize()
+        r.check_kernel_errors()
+        r.cache.check_invariants()
+        outs[fused] = whole
+    assert rel_err(outs[True], outs[False]) <= TOL["bfloat16"] / 2
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_whole_tail_and_portions(models, name, dtype):
