@@ -194,8 +194,9 @@ def decode_device_timed(engine, batch, steps, warmup, vocab, seed, context=CONTE
     return ms / steps, launches, (w0, w1)
 
 
-def decode_e2e(engine, batch, steps, warmup, vocab, seed):
-    """The same decode steps through the public entry point: host token ids in and out."""
+def decode_e2e(engine, batch, steps, warmup, vocab, seed, trace=False):
+    """The same decode steps through the public entry point: host token ids in and out.  With
+    `trace`, `engine.stats.host_seconds` holds the host's time in the timed steps afterwards."""
     import random
     import torch
     from rustinfer_b200.sampling.params import SamplingParams
@@ -213,6 +214,9 @@ def decode_e2e(engine, batch, steps, warmup, vocab, seed):
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
+    if trace:
+        engine.stats.host_seconds.clear()
+        engine.trace_host = True
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     w0 = time.time()
     e0.record()
@@ -220,6 +224,7 @@ def decode_e2e(engine, batch, steps, warmup, vocab, seed):
     for _ in range(steps - 1):
         got += len(engine.step())
     e1.record()
+    engine.trace_host = False
     torch.cuda.synchronize()
     w1 = time.time()
     ms = e0.elapsed_time(e1) / (steps - 1)
@@ -466,10 +471,11 @@ def main() -> int:
                     help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--skip-points", action="store_true", help="leave out everything under `points`")
     ap.add_argument("--repeats", type=int, default=5, help="timed windows of the headline (the median is reported)")
-    ap.add_argument("--only", choices=["decode", "prefill", "serve"],
+    ap.add_argument("--only", choices=["decode", "prefill", "serve", "e2e"],
                     help="run one part alone and print its time (for profiler captures; no JSON line); "
                          "serve: 64 requests, prompts of 128 to 2,048 tokens, 256 tokens out each, "
-                         "prompt portions of 512, through Engine.generate")
+                         "prompt portions of 512, through Engine.generate; e2e: the decode steps through "
+                         "Engine.step with host tokens in and out, and where the host's time in a step goes")
     ap.add_argument("--eager", action="store_true", help="with --only decode: no CUDA graphs")
     ap.add_argument("--sampled", action="store_true",
                     help="with --only decode: every token drawn (temperature 0.8, top-k 50, top-p 0.9) instead of the argmax")
@@ -514,7 +520,18 @@ def main() -> int:
             engine = Engine(folder, dtype="bfloat16", max_batch_tokens=8192, max_batch_seqs=seqs,
                             max_model_len=longest, paged_block_size=PAGE, num_blocks=seqs * longest // PAGE + 64,
                             capture_sizes=[] if args.eager else [1, 2, 4, 8, 16, 32, 64], ignore_eos=True)
-            if args.only == "decode":
+            if args.only == "e2e":
+                decode_e2e(engine, args.batch, args.steps, args.warmup, vocab, 1)          # graphs captured: untimed
+                ms, _, _, _ = decode_e2e(engine, args.batch, args.steps, args.warmup, vocab, 2, trace=True)
+                host = dict(engine.stats.host_seconds)
+                ms_dev, _, _ = decode_device_timed(engine, args.batch, args.steps, args.warmup, vocab, 3)
+                print(f"e2e b{args.batch} layers{args.layers}: {ms:.4f} ms/step through Engine.step, {ms_dev:.4f} device-timed")
+                n = args.steps - 1
+                for what, sec in host.items():
+                    print(f"  host, {what}: {sec / n * 1e6:8.1f} us a step")
+                busy = sum(sec for what, sec in host.items() if not what.startswith("wait"))
+                print(f"  host busy {busy / n * 1e6:.1f} us of the step's {ms * 1e3:.1f} us; the rest it waits for the GPU")
+            elif args.only == "decode":
                 global_ctx = args.context
                 sp = None
                 if args.sampled:

@@ -61,6 +61,10 @@ class EngineStats:
     preemptions: int = 0
     seconds: float = 0.0
     step_ms: List[float] = field(default_factory=list)
+    # with `Engine.trace_host` set: seconds the host spent in each part of `step`, summed over the
+    # steps (plan, entries, launch: the runner's step; choose: sampler and feedback launches;
+    # wait: blocked until the tokens of the step before were on the host; deliver)
+    host_seconds: Dict[str, float] = field(default_factory=dict)
 
 
 class Engine:
@@ -70,6 +74,7 @@ class Engine:
                  mem_fraction_static: float = 0.9, num_blocks: int = 0, ignore_eos: bool = False,
                  capture_sizes: Optional[Sequence[int]] = None):
         self.ignore_eos = ignore_eos
+        self.trace_host = False             # True: `stats.host_seconds` says where the host's time in `step` goes
         self.chunked_prefill_size = chunked_prefill_size
         if num_blocks <= 0:
             num_blocks = None
@@ -135,6 +140,9 @@ class Engine:
         sched = self.scheduler
         outs: List[StepOutput] = []
         before = sched.num_preemptions
+        clock = time.perf_counter
+        trace = self.stats.host_seconds if self.trace_host else None
+        t_a = clock()
         plan = sched.schedule()
         self.stats.preemptions += sched.num_preemptions - before
         chain = self._inflight is not None and self._chainable(plan)
@@ -156,8 +164,11 @@ class Engine:
             entries.append(StepEntry(req.request_id, toks, [e.count - 1] if e.samples else []))
             if e.samples:
                 samplers.append(req)
-        t0 = time.perf_counter()
+        t0 = clock()
+        if trace is not None:
+            trace["plan and entries"] = trace.get("plan and entries", 0.0) + (t0 - t_a)
         logits = r.step(entries, device_tokens=self._feed if chain else None, borrow_logits=True)
+        t_b = clock()
         launched = None
         if samplers:
             n = len(samplers)
@@ -171,6 +182,10 @@ class Engine:
             ev.record()
             launched = _InFlight(plan, samplers, k, ev, True)
         sched.advance(plan)
+        t_c = clock()
+        if trace is not None:
+            trace["launch (runner.step)"] = trace.get("launch (runner.step)", 0.0) + (t_b - t0)
+            trace["choose and feed back"] = trace.get("choose and feed back", 0.0) + (t_c - t_b)
         self.stats.steps += 1
         self.stats.chained_steps += 1 if chain else 0
         self.stats.prompt_tokens += sum(e.count for e in plan.entries) - sum(
@@ -195,7 +210,11 @@ class Engine:
     def _resolve(self) -> List[StepOutput]:
         """Wait for the tokens of the step in flight, hand them to the scheduler."""
         f, self._inflight = self._inflight, None
+        t_w = time.perf_counter()
         f.event.synchronize()
+        if self.trace_host:
+            h = self.stats.host_seconds
+            h["wait for the step before"] = h.get("wait for the step before", 0.0) + (time.perf_counter() - t_w)
         n = len(f.samplers)
         res = self._result_host[f.turn][: 2 * n].tolist()
         tokens, stops = res[:n], res[n:]

@@ -38,7 +38,7 @@ WAITING, PREFILL, DECODE, FINISHED = "waiting", "prefill", "decode", "finished"
 DRAINING = "draining"     # its last token is chosen but not yet delivered to the host: nothing more to run
 
 
-@dataclass
+@dataclass(eq=False)                     # a request is itself: lists of them are searched by identity, not by comparing prompts
 class Request:
     request_id: Any
     prompt: List[int]
