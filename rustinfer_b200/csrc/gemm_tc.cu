@@ -257,7 +257,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // the even stage and then fills both.
         bool ok = true;
         int it = 0, s = 0;                                // k-blocks loaded so far, over all tiles; ring position
-        unsigned par = 1;                                 // parity of the release this round waits for
+        unsigned par = 1;                                 // parity of the release the current lap of the ring waits for
         for (int tile = blockIdx.x; tile < p.n_tiles && ok; tile += gridDim.x) {
             const int a0 = (tile % p.tiles_a) * p.a_box, b0 = (tile / p.tiles_a) * BN;
             const int w0 = p.swap ? a0 : b0, x0 = p.swap ? b0 : a0;
