@@ -567,7 +567,7 @@ def main() -> int:
         points = {}
         if not args.skip_points:
             from rustinfer_b200.sampling.params import SamplingParams
-            k = args.steps
+            k = max(args.steps, 64)                       # (the headline keeps exactly --steps; these are its company)
             for b in (1, 64):
                 (ms_b, _, w), _all = median_of(lambda: decode_device_timed(engine, b, k, args.warmup, vocab, next(seeds)), 3)
                 windows.append(w)
@@ -663,7 +663,7 @@ def further_shapes(args, hbm_gbs, bf16_tflops, windows, say):
     seeds = iter(range(20_000, 30_000))
     # (windows as long as the headline's: the steps right after the burst that fills the context run
     # several per cent slower than the ones that follow, and a short window is mostly those)
-    k = args.steps
+    k = max(args.steps, 64)
     # ---- Llama-3.1-8B-shaped, 8 of 32 layers
     name, shape = SHAPES["8b"]
     layers = 8
