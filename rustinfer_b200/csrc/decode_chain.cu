@@ -316,11 +316,15 @@ decode_chain_kernel(const __grid_constant__ Maps maps, const __grid_constant__ P
                     const unsigned nw_bytes = (unsigned)Kc * (nw_bf16 ? 2u : 4u);
                     for (int r0 = 0; r0 < M && ok; r0 += p.stage_rows) {
                         const int rows = min(p.stage_rows, M - r0);
-                        if (threadIdx.x == 64) {
-                            mbar_expect_tx(x_land, (unsigned)rows * P.K * 4u + (nw_here ? 0u : nw_bytes));
-                            for (int r = 0; r < rows; ++r)
-                                bulk_load(stg + (size_t)r * P.K, hs + (size_t)(r0 + r) * P.ld_x, (unsigned)P.K * 4u, x_land);
-                            if (!nw_here) bulk_load(nws, P.norm_w, nw_bytes, x_land);
+                        if (warp == 2) {
+                            // a row's copy from a lane of its own (one thread sends a copy every 74 ns; nine
+                            // from one thread were 0.7 us of each of the chain's two stagings)
+                            if (lane == 0) mbar_expect_tx(x_land, (unsigned)rows * P.K * 4u + (nw_here ? 0u : nw_bytes));
+                            __syncwarp();
+                            if (lane < rows)
+                                bulk_load(stg + (size_t)lane * P.K, hs + (size_t)(r0 + lane) * P.ld_x, (unsigned)P.K * 4u, x_land);
+                            else if (lane == rows && !nw_here)
+                                bulk_load(nws, P.norm_w, nw_bytes, x_land);
                         }
                         nw_here = true;
                         ok = mbar_wait(x_land, xl & 1, p.error, ERR_CHAIN_EPILOGUE);
