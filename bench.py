@@ -161,7 +161,8 @@ def decode_device_timed(engine, batch, steps, warmup, vocab, seed, context=CONTE
     from rustinfer_b200.engine.runner import StepEntry
     from rustinfer_b200.ops import library
     r = engine.runner
-    ctx0 = context - (steps + warmup + SETTLE_STEPS)
+    settle = min(SETTLE_STEPS, max(0, context - (steps + warmup) - 16))     # (a short context leaves less room)
+    ctx0 = context - (steps + warmup + settle)
     ids = fill_context(engine, batch, ctx0, vocab, seed)
     tokens = torch.randint(0, vocab, (batch,), dtype=torch.int32, device=r.device)
     entries = [StepEntry(rid, [0], [0]) for rid in ids]
@@ -179,7 +180,7 @@ def decode_device_timed(engine, batch, steps, warmup, vocab, seed, context=CONTE
 
     r_step = r.step
     r.step = lambda e, device_tokens=None: r_step(e, device_tokens=device_tokens, borrow_logits=True)
-    for _ in range(SETTLE_STEPS + warmup):
+    for _ in range(settle + warmup):
         one()
     torch.cuda.synchronize()
     l0 = library.launch_count
